@@ -28,7 +28,7 @@ from ..cache import manager as cache_mod
 from ..kernels import ops
 from ..models.builder import CausalLM, load_model
 from ..parts.base import CacheView, GroupView, StepContext
-from ..parts.spec import FixedState, PagedKV
+from ..parts.spec import FixedState, PagedKV, PagedLatent
 from .. import profiling
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32,
@@ -98,19 +98,30 @@ class Engine:
         self.cache = rt.CacheManager(groups, self.max_requests)
         self.group_windows = list(plan.group_windows)
         self.views: list[CacheView] = []
-        for need, group in zip(plan.needs, plan.group_of):
-            if isinstance(need, PagedKV):
+        for need, block_need, group in zip(plan.needs, plan.block_needs, plan.group_of):
+            block_state = None
+            if isinstance(block_need, FixedState):
+                block_state = torch.zeros((self.max_requests,) + tuple(block_need.shape), dtype=torch.float32,
+                                          device=self.device)
+            elif block_need is not None:
+                raise ValueError("a block arrangement may keep fixed-size state only")
+            if isinstance(need, PagedLatent):
+                latent = torch.empty((self.num_pages, self.page_size, need.width), dtype=self.dtype, device=self.device)
+                self.views.append(CacheView(need, group=group, k=latent, block_state=block_state))
+            elif isinstance(need, PagedKV):
                 shape = (self.num_pages, need.n_kv_heads, self.page_size, need.head_dim)
                 # Pages are never cleared: what may be read is decided by lengths alone.
                 k = torch.empty(shape, dtype=self.dtype, device=self.device)
                 v = torch.empty(shape, dtype=self.dtype, device=self.device)
-                self.views.append(CacheView(need, group=group, k=k, v=v))
+                self.views.append(CacheView(need, group=group, k=k, v=v, block_state=block_state))
             elif isinstance(need, FixedState):
                 state = torch.zeros((self.max_requests,) + tuple(need.shape), dtype=torch.float32, device=self.device)
-                self.views.append(CacheView(need, state=state))
+                self.views.append(CacheView(need, state=state, block_state=block_state))
             else:
-                self.views.append(CacheView(None))
-        self.stateful = any(v.state is not None for v in self.views)
+                self.views.append(CacheView(None, block_state=block_state))
+        # every tensor of fixed-size per-request state, the mixers' and the blocks' own
+        self.state_tensors = [t for v in self.views for t in (v.state, v.block_state) if t is not None]
+        self.stateful = bool(self.state_tensors)
         self.max_blocks = -(-self.max_seq_len // self.page_size)
         self.stats = EngineStats()
         self._staging = [self._new_staging() for _ in range(3)]
@@ -151,9 +162,8 @@ class Engine:
         """A new request: takes a state slot.  Its fixed-size state is cleared here and again by the
         first step that brings it tokens (the scheduler opens requests without the engine)."""
         slot = self.cache.open(int(request))
-        for view in self.views:
-            if view.state is not None:
-                view.state[slot].zero_()
+        for state in self.state_tensors:
+            state[slot].zero_()
 
     def close(self, request: int) -> None:
         """The request ends; its pages and its state slot may be used again."""
@@ -253,12 +263,10 @@ class Engine:
                                      device=self.device)
                 fresh = [i for i, (r, _) in enumerate(pairs) if self.cache.length(r) == 0]
                 saved = []
-                for view in self.views:
-                    if view.state is None:
-                        continue
+                for state in self.state_tensors:
                     if fresh:
-                        view.state[slots[fresh]] = 0
-                    saved.append((view.state, slots, view.state[slots]))
+                        state[slots[fresh]] = 0
+                    saved.append((state, slots, state[slots]))
         except Exception:
             self._fail((opened, taken, None))
             raise

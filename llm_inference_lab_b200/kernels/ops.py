@@ -583,25 +583,26 @@ def _tc_operands(x, w) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def linear(x, w, bias=None, out_f32=False, allow_partial=False):
+def linear(x, w, bias=None, out_f32=False, allow_partial=False, out=None):
     """x @ w.T (+ bias).  With `allow_partial` the result may come back as 32-bit partial
     products [splits, tokens, out], without the bias, that the consumer sums (`add_rmsnorm`,
-    `rope_kv_write`)."""
-    if x.dtype == torch.float32 or _force_plain or not _tc_operands(x, w):
-        return gemm_plain(x, w, bias, out_f32=out_f32)
+    `rope_kv_write`, `stream_add`).  `out`: where the result goes (rows may be strided)."""
+    if x.dtype == torch.float32 or _force_plain or not _tc_operands(x, w) or (
+            out is not None and (out.stride(0) % 8 or out.data_ptr() % 16)):
+        return gemm_plain(x, w, bias, out_f32=out_f32, out=out)
     T = x.shape[0]
     if T > 128:
         kind, bn, splits = _pick_prefill_tiles(T, w.shape[0], x.shape[1],
-                                               allow_partial and bias is None and not out_f32)
+                                               allow_partial and bias is None and out is None)
         if kind == "pair":
-            return gemm_tc2(x, w, bias, out_f32=out_f32)
+            return gemm_tc2(x, w, bias, out_f32=out_f32, out=out)
         if splits > 1:
             return gemm_tc(x, w, None, swap=False, bn=bn, splits=splits)
-        return gemm_tc(x, w, bias, out_f32=out_f32, swap=False, bn=bn)
-    splits = _pick_splits(T, w.shape[0], x.shape[1]) if allow_partial else 1
+        return gemm_tc(x, w, bias, out_f32=out_f32, swap=False, bn=bn, out=out)
+    splits = _pick_splits(T, w.shape[0], x.shape[1]) if allow_partial and out is None else 1
     if splits > 1:
         return gemm_tc(x, w, None, splits=splits)     # the consumer adds the bias
-    return gemm_tc(x, w, bias, out_f32=out_f32)
+    return gemm_tc(x, w, bias, out_f32=out_f32, out=out)
 
 
 def linear_gated(x, w_gate_up):
@@ -720,3 +721,207 @@ def attention(q, cache_k, cache_v, ctx, group, n_q, n_kv, head_dim, window, scal
                             ctx.n_requests, ctx.q_lens, ctx.max_kv_len, n_q, n_kv, head_dim, window, scale)
     return attention_plain(q, cache_k, cache_v, ctx.row_req, ctx.row_pos, group.block_table, n_q, n_kv, head_dim,
                            window, scale)
+
+
+# ----------------------------------------------------------------------------------------
+# Operators on a residual stream kept in 32-bit floats (csrc/kernels/stream32.cu).
+# ----------------------------------------------------------------------------------------
+def embed_norm(ids: torch.Tensor, table: torch.Tensor, weight: torch.Tensor, eps: float, offset: float) -> torch.Tensor:
+    """32-bit rows table[id] / rms(table[id]) * (offset + weight)."""
+    _on_gpu(ids, table, weight)
+    tokens, (vocab, hidden) = ids.numel(), table.shape
+    assert ids.dtype == torch.int32 and table.is_contiguous() and weight.dtype == table.dtype
+    out = torch.empty((tokens, hidden), dtype=torch.float32, device=table.device)
+    _check(lib("stream32").lab_embed_norm(_ptr(out), _ptr(table), _ptr(ids), _ptr(weight), tokens, hidden, vocab,
+                                          ctypes.c_float(eps), ctypes.c_float(offset), dtype_code(table.dtype),
+                                          _stream()), "embed_norm")
+    return out
+
+
+def norm_stream(x: torch.Tensor, eps: float, offset: float, weight_f32: torch.Tensor | None = None,
+                weight: torch.Tensor | None = None, rows: torch.Tensor | None = None):
+    """RMS norms of the rows of a 32-bit stream `x`, gain (offset + weight): with `weight_f32` a 32-bit
+    result, with `weight` one rounded to the weight's storage type; both at once read x once.  With
+    `rows`, output row i comes from x[rows[i]].  Returns (32-bit result or None, stored result or None)."""
+    _on_gpu(x, weight_f32, weight, rows)
+    n_in, hidden = x.shape
+    n_out = n_in if rows is None else rows.numel()
+    assert x.dtype == torch.float32 and x.is_contiguous() and (weight_f32 is not None or weight is not None)
+    wdt = (weight if weight is not None else weight_f32).dtype
+    assert weight_f32 is None or weight is None or weight_f32.dtype == weight.dtype
+    out_a = torch.empty((n_out, hidden), dtype=torch.float32, device=x.device) if weight_f32 is not None else None
+    out_b = torch.empty((n_out, hidden), dtype=wdt, device=x.device) if weight is not None else None
+    _check(lib("stream32").lab_norm_stream(_ptr(out_a), _ptr(out_b), _ptr(x), _ptr(weight_f32), _ptr(weight), _ptr(rows),
+                                           n_out, n_in, hidden, ctypes.c_float(eps), ctypes.c_float(offset),
+                                           dtype_code(wdt), _stream()), "norm_stream")
+    return out_a, out_b
+
+
+def token_shift(normed: torch.Tensor, mix: torch.Tensor, kept: torch.Tensor, ctx, write: bool = True) -> torch.Tensor:
+    """h[t] = n[t] + (n[t-1] - n[t]) * mix over the rows of each request, the row before a request's
+    first row of this step taken from `kept` [slots, hidden] (zeros at position 0); `kept` then takes the
+    request's last row.  `normed` is 32-bit; the result has mix's storage type."""
+    _on_gpu(normed, mix, kept)
+    tokens, hidden = normed.shape
+    assert normed.dtype == torch.float32 and normed.is_contiguous() and kept.dtype == torch.float32
+    assert kept.is_contiguous() and kept.shape[1] == hidden and mix.numel() == hidden
+    out = torch.empty((tokens, hidden), dtype=mix.dtype, device=normed.device)
+    _check(lib("stream32").lab_token_shift(_ptr(out), _ptr(normed), _ptr(mix), _ptr(kept), _ptr(ctx.row_req),
+                                           _ptr(ctx.q_start), _ptr(ctx.pos0), _ptr(ctx.state_slot), tokens, hidden,
+                                           kept.shape[0], int(write), dtype_code(mix.dtype), _stream()), "token_shift")
+    return out
+
+
+def stream_add(x: torch.Tensor, a: torch.Tensor, scale_a: torch.Tensor, b: torch.Tensor | None,
+               scale_b: torch.Tensor | None, mult: float) -> torch.Tensor:
+    """x += mult * (scale_a * a + scale_b * b) in place on the 32-bit stream; a and b are 32-bit products
+    [tokens, hidden] or split-K partial products [splits, tokens, hidden] (summed in ascending order)."""
+    _on_gpu(x, a, b, scale_a, scale_b)
+    tokens, hidden = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous()
+
+    def splits_of(t):
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.shape[-2:] == x.shape
+        return t.shape[0] if t.dim() == 3 else 1
+
+    sa = splits_of(a)
+    sb = splits_of(b) if b is not None else 0
+    assert scale_a.numel() == hidden and (b is None or (scale_b.numel() == hidden and scale_b.dtype == scale_a.dtype))
+    _check(lib("stream32").lab_stream_add(_ptr(x), _ptr(a), sa, _ptr(b), sb, _ptr(scale_a), _ptr(scale_b),
+                                          ctypes.c_longlong(tokens), hidden, ctypes.c_float(mult),
+                                          dtype_code(scale_a.dtype), _stream()), "stream_add")
+    return x
+
+
+def stream_concat(x: torch.Tensor, x0: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """[x ; x0] row by row, rounded to `dtype`, for a projection that reads both."""
+    _on_gpu(x, x0)
+    tokens, hidden = x.shape
+    assert x.dtype == torch.float32 and x0.dtype == torch.float32 and x.is_contiguous() and x0.is_contiguous()
+    assert x0.shape == x.shape
+    out = torch.empty((tokens, 2 * hidden), dtype=dtype, device=x.device)
+    _check(lib("stream32").lab_stream_concat(_ptr(out), _ptr(x), _ptr(x0), ctypes.c_longlong(tokens), hidden,
+                                             dtype_code(dtype), _stream()), "stream_concat")
+    return out
+
+
+def softcap(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """logits <- cap * tanh(logits / cap), in place on 32-bit logits."""
+    _on_gpu(logits)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    _check(lib("stream32").lab_softcap(_ptr(logits), ctypes.c_longlong(logits.numel()), ctypes.c_float(cap), _stream()),
+           "softcap")
+    return logits
+
+
+# ----------------------------------------------------------------------------------------
+# Generalized delta rule (csrc/kernels/delta_rule.cu, built per head size).
+# ----------------------------------------------------------------------------------------
+def delta_rule_supported(head_dim: int) -> bool:
+    return 4 <= head_dim <= 256
+
+
+def tanh_cast(x: torch.Tensor, dtype: torch.dtype, head_dim: int = 64) -> torch.Tensor:
+    """tanh of a 32-bit column slice [tokens, n], rounded to `dtype` and made contiguous (`head_dim`
+    names the build of the delta rule's library to take it from)."""
+    _on_gpu(x)
+    tokens, n = x.shape
+    assert x.dtype == torch.float32 and x.stride(1) == 1
+    out = torch.empty((tokens, n), dtype=dtype, device=x.device)
+    _check(lib("delta_rule", {"LAB_HEAD_DIM": head_dim}).lab_tanh_cast(_ptr(out), _ptr(x), ctypes.c_longlong(tokens), n,
+                                                                 x.stride(0), dtype_code(dtype), _stream()),
+           "tanh_cast")
+    return out
+
+
+def delta_rule(proj: torch.Tensor, decay_pre: torch.Tensor, decay_bias: torch.Tensor, rate_bias: torch.Tensor,
+               norm_weight: torch.Tensor, state: torch.Tensor, ctx, heads: int, head_dim: int, eps: float,
+               decay_rate: float, write: bool = True) -> torch.Tensor:
+    """The recurrence over each request's rows.  `proj` [tokens, >= 5 * heads * head_dim] 32-bit holds
+    r, k, v, the gate's and the removal rate's pre-activations side by side; `decay_pre` [tokens,
+    heads * head_dim] the decay's; `state` [slots, heads, head_dim, head_dim] 32-bit is read and (with
+    `write`) left advanced.  Returns the normalised, gated output in the biases' storage type."""
+    _on_gpu(proj, decay_pre, decay_bias, rate_bias, norm_weight, state)
+    tokens, hd = proj.shape[0], heads * head_dim
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= 5 * hd
+    assert decay_pre.dtype == torch.float32 and decay_pre.stride(1) == 1 and decay_pre.shape == (tokens, hd)
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, head_dim, head_dim)
+    dt = decay_bias.dtype
+    assert rate_bias.dtype == dt and norm_weight.dtype == dt
+    assert decay_bias.numel() == hd and rate_bias.numel() == hd and norm_weight.numel() == hd
+    if not delta_rule_supported(head_dim):
+        raise KernelError(f"delta_rule: head size {head_dim} outside 4..256")
+    out = torch.empty((tokens, hd), dtype=dt, device=proj.device)
+    L = lib("delta_rule", {"LAB_HEAD_DIM": head_dim})
+    base, esz = proj.data_ptr(), 4
+
+    def col(i):
+        return ctypes.c_void_p(base + esz * i * hd)
+
+    _check(L.lab_delta_rule(_ptr(out), col(0), col(1), col(2), col(3), col(4), proj.stride(0), _ptr(decay_pre),
+                            decay_pre.stride(0), _ptr(decay_bias), _ptr(rate_bias), _ptr(norm_weight), _ptr(state),
+                            _ptr(ctx.q_start), _ptr(ctx.state_slot), ctx.n_requests, heads, state.shape[0], int(write),
+                            ctypes.c_float(eps), ctypes.c_float(decay_rate), dtype_code(dt), _stream()), "delta_rule")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# Attention over a paged cache of latents (csrc/kernels/latent_attention.cu).
+# ----------------------------------------------------------------------------------------
+def latent_prep(proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, w_q: torch.Tensor, w_c: torch.Tensor,
+                positions: torch.Tensor, inv_freq: torch.Tensor, rot_dims: int, slots: torch.Tensor | None,
+                cache: torch.Tensor | None, eps: float) -> torch.Tensor:
+    """From the 32-bit low-rank projections of a step's rows [tokens, q_rank + kv_rank + rot_dim]: the
+    normalised query latent (returned, in the weights' storage type), and, into each row's cache slot,
+    the normalised key/value latent followed by the rotated shared key part (`cache` None: no write)."""
+    _on_gpu(proj, w_q, w_c, positions, inv_freq, slots, cache)
+    tokens = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] == q_rank + kv_rank + rot_dim
+    assert w_q.numel() == q_rank and w_c.numel() == kv_rank and w_q.dtype == w_c.dtype
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2 and rot_dims <= rot_dim
+    n_slots = 0
+    if cache is not None:
+        assert cache.is_contiguous() and cache.shape[2] == kv_rank + rot_dim and cache.dtype == w_q.dtype
+        assert slots is not None and slots.dtype == torch.int32
+        n_slots = cache.shape[0] * cache.shape[1]
+    cq = torch.empty((tokens, q_rank), dtype=w_q.dtype, device=proj.device)
+    _check(lib("latent_attention").lab_latent_prep(
+        _ptr(cq), _ptr(cache), _ptr(proj), proj.stride(0), q_rank, kv_rank, rot_dim, _ptr(w_q), _ptr(w_c),
+        _ptr(positions), _ptr(inv_freq), rot_dims, _ptr(slots), ctypes.c_longlong(n_slots), tokens,
+        ctypes.c_float(eps), dtype_code(w_q.dtype), _stream()), "latent_prep")
+    return cq
+
+
+def latent_q_rope(q: torch.Tensor, q_cat: torch.Tensor, heads: int, dim: int, rot_dim: int, kv_rank: int,
+                  positions: torch.Tensor, inv_freq: torch.Tensor, rot_dims: int) -> None:
+    """Rotates the last `rot_dim` entries of every head of q [tokens, heads * (dim + rot_dim)] into
+    columns [kv_rank, kv_rank + rot_dim) of each head of the 32-bit q_cat [tokens, heads, kv_rank + rot_dim]."""
+    _on_gpu(q, q_cat, positions, inv_freq)
+    tokens = q.shape[0]
+    assert q.is_contiguous() and q.shape[1] == heads * (dim + rot_dim)
+    assert q_cat.dtype == torch.float32 and q_cat.is_contiguous() and q_cat.shape == (tokens, heads, kv_rank + rot_dim)
+    _check(lib("latent_attention").lab_latent_q_rope(_ptr(q_cat), _ptr(q), tokens, heads, dim, rot_dim, kv_rank,
+                                                     _ptr(positions), _ptr(inv_freq), rot_dims, dtype_code(q.dtype),
+                                                     _stream()), "latent_q_rope")
+
+
+def latent_attention(q_cat: torch.Tensor, cache: torch.Tensor, sink: torch.Tensor | None, ctx, group, heads: int,
+                     kv_rank: int, window: int, scale: float) -> torch.Tensor:
+    """Every row's heads over the latents of its request's pages: scores q_cat . [c ; kr] * scale,
+    softmax in 32-bit whose denominator also holds exp(sink) per head, output the weighted sum of the
+    latents c, [tokens, heads * kv_rank] in the cache's storage type."""
+    _on_gpu(q_cat, cache, sink)
+    tokens, width = q_cat.shape[0], q_cat.shape[2]
+    num_pages, page_size, w = cache.shape
+    assert w == width and cache.is_contiguous() and q_cat.dtype == torch.float32 and q_cat.is_contiguous()
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == heads)
+    L = lib("latent_attention")
+    if L.lab_latent_attention_rows(heads, kv_rank, width, ctx.max_q_len) <= 0:
+        raise KernelError(f"latent_attention: {heads} heads of width {width} do not fit shared memory")
+    out = torch.empty((tokens, heads * kv_rank), dtype=cache.dtype, device=cache.device)
+    table = group.block_table
+    _check(L.lab_latent_attention(_ptr(out), _ptr(q_cat), _ptr(cache), _ptr(sink), _ptr(ctx.q_start), _ptr(ctx.pos0),
+                                  _ptr(table), table.shape[1], ctx.n_requests, ctx.max_q_len, heads, kv_rank, width,
+                                  page_size, num_pages, window, ctypes.c_float(scale), dtype_code(cache.dtype),
+                                  _stream()), "latent_attention")
+    return out

@@ -16,7 +16,7 @@ import torch
 
 from ..parts.base import CacheView, StepContext, lookup
 from ..profiling import scoped_range
-from ..parts.spec import CacheNeed, ModelBlueprint, PagedKV, TensorSpec
+from ..parts.spec import CacheNeed, ModelBlueprint, PagedKV, PagedLatent, TensorSpec
 
 
 # False: pure decode steps run part by part as every other step does (tests compare the two).
@@ -27,9 +27,13 @@ def _part_classes(bp: ModelBlueprint):
     yield lookup("embedding", bp.embedding.kind), bp.embedding
     for layer in bp.layers:
         yield lookup("mixer", layer.mixer.kind), layer.mixer
-        yield lookup("feed_forward", layer.ffn.kind), layer.ffn
+        if layer.ffn is not None:
+            yield lookup("feed_forward", layer.ffn.kind), layer.ffn
         for n in layer.norms:
             yield lookup("norm", n.kind), n
+        yield lookup("block", layer.block), layer.block_spec
+    for entry in bp.reentries:
+        yield lookup("reentry", entry.part.kind), entry.part
     yield lookup("norm", bp.final_norm.kind), bp.final_norm
     yield lookup("head", bp.head.kind), bp.head
 
@@ -49,6 +53,7 @@ def expected_tensors(bp: ModelBlueprint) -> list[TensorSpec]:
 class CachePlan:
     """What the caches of a model look like: one need per cache id, gathered in groups."""
     needs: tuple[CacheNeed, ...]            # by cache id
+    block_needs: tuple[CacheNeed, ...]      # by cache id: fixed-size state of the block arrangement itself
     group_of: tuple[int, ...]               # cache id -> group index (-1: no paged group)
     group_windows: tuple[int, ...]          # per paged group: 0 or the window
 
@@ -56,10 +61,15 @@ class CachePlan:
 def cache_plan(bp: ModelBlueprint) -> CachePlan:
     n_caches = 1 + max((c.cache for c in bp.order), default=-1)
     needs: list = [None] * n_caches
+    block_needs: list = [None] * n_caches
     writers = [0] * n_caches
     for call in bp.order:
         layer = bp.layers[call.layer]
         need = lookup("mixer", layer.mixer.kind).cache_need(layer.mixer)
+        block_need = lookup("block", layer.block).cache_need(layer.block_spec)
+        if block_needs[call.cache] is not None and block_needs[call.cache] != block_need:
+            raise ValueError(f"cache {call.cache} is used by blocks with different needs")
+        block_needs[call.cache] = block_need
         if needs[call.cache] is not None and needs[call.cache] != need:
             raise ValueError(f"cache {call.cache} is used by layers with different needs: "
                              f"{needs[call.cache]} and {need}")
@@ -71,19 +81,20 @@ def cache_plan(bp: ModelBlueprint) -> CachePlan:
     keys: list = []
     group_of = []
     for need in needs:
-        if isinstance(need, PagedKV):
+        if isinstance(need, (PagedKV, PagedLatent)):
             key = need.group_key()
             if key not in keys:
                 keys.append(key)
             group_of.append(keys.index(key))
         else:
             group_of.append(-1)
-    return CachePlan(tuple(needs), tuple(group_of), tuple(k[1] for k in keys))
+    return CachePlan(tuple(needs), tuple(block_needs), tuple(group_of), tuple(k[1] for k in keys))
 
 
 class CausalLM:
     """Embedding, blocks in the blueprint's order, final norm, head."""
 
+    reentries: dict = {}    # run index -> what is done to the stream right before that layer call
     decode_stack = None     # the one kernel that runs all layer calls of a small decode step, where the layers fit it
 
     def __init__(self, bp: ModelBlueprint, weights: dict[str, torch.Tensor], dtype: torch.dtype, device):
@@ -93,9 +104,13 @@ class CausalLM:
         self.blocks = []
         for layer in bp.layers:
             mixer = lookup("mixer", layer.mixer.kind)(layer.mixer, weights, dtype, device)
-            ffn = lookup("feed_forward", layer.ffn.kind)(layer.ffn, weights, dtype, device)
+            ffn = None
+            if layer.ffn is not None:
+                ffn = lookup("feed_forward", layer.ffn.kind)(layer.ffn, weights, dtype, device)
             norms = [lookup("norm", n.kind)(n, weights, dtype, device) for n in layer.norms]
-            self.blocks.append(lookup("block", layer.block)(mixer, ffn, norms))
+            self.blocks.append(lookup("block", layer.block)(mixer, ffn, norms, layer.block_spec, weights, dtype, device))
+        self.reentries = {e.before: lookup("reentry", e.part.kind)(e.part, weights, dtype, device)
+                          for e in bp.reentries}
         self.final_norm = lookup("norm", bp.final_norm.kind)(bp.final_norm, weights, dtype, device)
         self.head = lookup("head", bp.head.kind)(bp.head, weights, dtype, device)
         self.order = bp.order
@@ -119,7 +134,15 @@ class CausalLM:
             calls = ()
         else:
             calls = zip(self.order, self.range_names)
-        for call, name in calls:
+        # blocks may add to the stream in place: a re-entry reads a copy of the embedding output
+        x0 = x.clone() if self.reentries else None
+        for index, (call, name) in enumerate(calls):
+            entry = self.reentries.get(index)
+            if entry is not None:
+                if pending is not None:
+                    raise ValueError("a re-entry follows a block that leaves part of its sum to the next norm")
+                with scoped_range("reentry"):
+                    x = entry.forward(x, x0)
             view = caches[call.cache]
             if not call.write:
                 view = dataclasses.replace(view, write=False)

@@ -14,6 +14,7 @@ registry           interface
 ``BLOCKS``         `Block`: ``forward(x, pending, ctx, cache)``
 ``EMBEDDINGS``     `Embedding`: ``forward(token_ids)``
 ``HEADS``          `Head`: ``forward(x)`` giving 32-bit logits
+``REENTRIES``      `StreamReentry`: ``forward(x, x0)`` between two layer calls
 =================  ==========================================================
 
 `x` is the packed batch ``[tokens, hidden]``: rows of all requests of the step,
@@ -69,9 +70,10 @@ class CacheView:
     need: CacheNeed
     group: int = -1                         # index into StepContext.groups (paged caches)
     write: bool = True                      # False: the call only reads what another call wrote
-    k: Optional[torch.Tensor] = None        # [pages, n_kv, page_size, head_dim]
+    k: Optional[torch.Tensor] = None        # [pages, n_kv, page_size, head_dim]; a paged latent: [pages, page_size, width]
     v: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None    # [max_requests, *shape] float32
+    block_state: Optional[torch.Tensor] = None   # fixed-size state of the block arrangement itself, same form
 
 
 class Part:
@@ -143,14 +145,32 @@ class PositionEncoding(Part):
 class Block:
     kind = ""
 
-    def __init__(self, mixer: Mixer, ffn: FeedForward, norms: list[Norm]):
-        self.mixer, self.ffn, self.norms = mixer, ffn, norms
+    @classmethod
+    def tensors(cls, spec: Optional[PartSpec]) -> list[TensorSpec]:
+        """Tensors of the arrangement itself (per-channel scales and the like); most have none."""
+        return []
+
+    @classmethod
+    def cache_need(cls, spec: Optional[PartSpec]) -> CacheNeed:
+        """Fixed-size state the arrangement itself keeps per request (beside the mixer's cache)."""
+        return None
+
+    def __init__(self, mixer: Mixer, ffn: Optional[FeedForward], norms: list[Norm], spec: Optional[PartSpec] = None,
+                 weights=None, dtype=None, device=None):
+        self.mixer, self.ffn, self.norms, self.spec = mixer, ffn, norms, spec
         # names of the profiling ranges around the two halves of a block
         self.mixer_range = "mixer." + str(getattr(getattr(mixer, "spec", None), "kind", type(mixer).__name__))
         self.ffn_range = "feed_forward." + str(getattr(getattr(ffn, "spec", None), "kind", type(ffn).__name__))
 
     def forward(self, x, pending, ctx: StepContext, cache: CacheView):
         """`pending` is what the previous block still owes the residual stream (or None)."""
+        raise NotImplementedError
+
+
+class StreamReentry(Part):
+    """Changes the residual stream between two layer calls, given the embedding output."""
+
+    def forward(self, x: torch.Tensor, x0: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -178,8 +198,9 @@ POSITIONS: dict[str, type] = {}
 BLOCKS: dict[str, type] = {}
 EMBEDDINGS: dict[str, type] = {}
 HEADS: dict[str, type] = {}
+REENTRIES: dict[str, type] = {}
 _REGISTRIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "position": POSITIONS,
-               "block": BLOCKS, "embedding": EMBEDDINGS, "head": HEADS}
+               "block": BLOCKS, "embedding": EMBEDDINGS, "head": HEADS, "reentry": REENTRIES}
 
 
 def register_part(family: str, kind: str, cls: type) -> type:

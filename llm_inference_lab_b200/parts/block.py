@@ -1,8 +1,13 @@
 """Arrangements of a mixer and a feed-forward around the residual stream."""
 from __future__ import annotations
 
+import torch
+
+from ..kernels import ops
 from ..profiling import scoped_range
 from .base import Block, register_part
+from .norm import StreamRMSNorm
+from .spec import FixedState, TensorSpec
 
 
 class PreNormBlock(Block):
@@ -24,3 +29,84 @@ class PreNormBlock(Block):
 
 
 register_part("block", "prenorm", PreNormBlock)
+
+
+class ParallelStreamBlock(Block):
+    """Mixer and feed-forward side by side on a 32-bit residual stream, each behind a norm of its own of
+    the same x:
+
+        x <- x + mult * (s1 * mixer(shift(norm1(x))) + s2 * ffn(norm2(x)))
+
+    Options, all parameters of the block's spec: `mult` (a constant), per-channel scales s1 and s2 of the
+    two results (`scale_names`), and a token shift of the mixer's input (`shift_name`): h[t] + (h[t-1] -
+    h[t]) * mix per channel, h[t-1] taken before its own shift, zeros before a sequence's first token.  The
+    last unshifted row of every request is fixed-size state of the block, beside the mixer's cache.  A layer
+    may have no feed-forward.  The sum is 32-bit; both results arrive as 32-bit products (or split-K partial
+    products, summed here)."""
+    n_norms = 2
+
+    @classmethod
+    def tensors(cls, spec):
+        out = []
+        if spec is None:
+            return out
+        h, p = spec["hidden"], spec.prefix
+        for name in spec.get("scale_names") or ():
+            out.append(TensorSpec(p + name, (h,), init="norm"))
+        if spec.get("shift_name"):
+            out.append(TensorSpec(p + spec["shift_name"], (h,), init="fraction"))
+        return out
+
+    @classmethod
+    def cache_need(cls, spec):
+        if spec is not None and spec.get("shift_name"):
+            return FixedState((spec["hidden"],))
+        return None
+
+    def __init__(self, mixer, ffn, norms, spec=None, weights=None, dtype=None, device=None):
+        super().__init__(mixer, ffn, norms, spec, weights, dtype, device)
+        if spec is None:
+            raise ValueError("parallel_stream: the block needs a spec (hidden, mult)")
+        h = spec["hidden"]
+
+        def get(name):
+            t = weights[spec.prefix + name]
+            return t if t.dtype == dtype else t.to(dtype)
+
+        names = tuple(spec.get("scale_names") or ())
+        if names and len(names) != (2 if ffn is not None else 1) and len(names) != 2:
+            raise ValueError("parallel_stream: one scale per result")
+        ones = None
+        if not names:
+            ones = torch.ones((h,), dtype=dtype, device=device)
+        self.scale_mixer = get(names[0]) if names else ones
+        self.scale_ffn = (get(names[1]) if names else ones) if ffn is not None else None
+        self.mix = get(spec["shift_name"]) if spec.get("shift_name") else None
+        self.mult = float(spec.get("mult", 1.0))
+        n1 = norms[0]
+        for n in norms[: 2 if ffn is not None else 1]:
+            if type(n) is not StreamRMSNorm or (n.eps, n.offset) != (n1.eps, n1.offset):
+                raise ValueError("parallel_stream: both norms are rmsnorm_stream with the same constants")
+
+    def forward(self, x, pending, ctx, cache):
+        if pending is not None:
+            raise ValueError("parallel_stream follows a block that leaves part of its sum to the next norm")
+        n1 = self.norms[0]
+        w2 = self.norms[1].weight if self.ffn is not None else None
+        with scoped_range(self.mixer_range):
+            if self.mix is not None:
+                normed, h2 = ops.norm_stream(x, n1.eps, n1.offset, weight_f32=n1.weight, weight=w2)
+                h1 = ops.token_shift(normed, self.mix, cache.block_state, ctx, write=cache.write)
+            else:
+                h1 = ops.norm_stream(x, n1.eps, n1.offset, weight=n1.weight)[1]
+                h2 = ops.norm_stream(x, n1.eps, n1.offset, weight=w2)[1] if w2 is not None else None
+            a = self.mixer.forward(h1, ctx, cache)
+        f = None
+        if self.ffn is not None:
+            with scoped_range(self.ffn_range):
+                f = self.ffn.forward(h2, ctx)
+        ops.stream_add(x, a, self.scale_mixer, f, self.scale_ffn, self.mult)
+        return x, None
+
+
+register_part("block", "parallel_stream", ParallelStreamBlock)

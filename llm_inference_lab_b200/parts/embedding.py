@@ -22,6 +22,28 @@ class TokenEmbedding(Embedding):
         return ops.embed(token_ids, self.table)
 
 
+class NormedTokenEmbedding(Embedding):
+    """x[t] = norm(table[id_t]) as a 32-bit residual stream: RMS norm with gain (offset + w), for
+    models that normalise right after the table and keep the stream in 32-bit."""
+
+    @classmethod
+    def tensors(cls, spec: PartSpec):
+        return [TensorSpec(spec["table"], (spec["vocab"], spec["hidden"]), init="table"),
+                TensorSpec(spec["norm"], (spec["hidden"],), init="around_zero" if spec.get("offset") else "norm")]
+
+    def __init__(self, spec, weights, dtype, device):
+        super().__init__(spec, weights, dtype, device)
+        t = weights[spec["table"]]
+        self.table = (t if t.dtype == dtype else t.to(dtype)).contiguous()
+        weights[spec["table"]] = self.table
+        w = weights[spec["norm"]]
+        self.weight = w if w.dtype == dtype else w.to(dtype)
+        self.eps, self.offset = float(spec["eps"]), float(spec.get("offset") or 0.0)
+
+    def forward(self, token_ids):
+        return ops.embed_norm(token_ids, self.table, self.weight, self.eps, self.offset)
+
+
 class LinearHead(Head):
     """logits = x W^T in 32-bit, no bias; W is the embedding table when tied
     (rust/engine/src/runner/model/qwen2/engine.rs:299-303, 1312-1319)."""
@@ -30,23 +52,28 @@ class LinearHead(Head):
     def tensors(cls, spec: PartSpec):
         if spec.get("tied_to"):
             return []
-        return [TensorSpec(spec.prefix + "weight", (spec["vocab"], spec["hidden"]))]
+        return [TensorSpec(spec.prefix + spec.get("name", "weight"), (spec["vocab"], spec["hidden"]))]
 
     def __init__(self, spec, weights, dtype, device):
         super().__init__(spec, weights, dtype, device)
         tied = spec.get("tied_to")
-        w = weights[tied] if tied else weights[spec.prefix + "weight"]
+        w = weights[tied] if tied else weights[spec.prefix + spec.get("name", "weight")]
         self.weight = (w if w.dtype == dtype else w.to(dtype)).contiguous()
+        # logits <- cap * tanh(logits / cap) where the model caps them (monotonic: the greedy pick is
+        # the same, a sampled one is not, so a capped head always forms its logits)
+        self.softcap = float(spec.get("softcap") or 0.0)
 
     def forward(self, x):
-        return ops.linear(x, self.weight, None, out_f32=True)
+        logits = ops.linear(x, self.weight, None, out_f32=True)
+        return ops.softcap(logits, self.softcap) if self.softcap else logits
 
     def pick(self, x, temperature, seeds, positions, out=None):
         # In one pass where the tensor-core product serves: the [rows, vocab] logits are never written.
-        if ops.head_pick_fusable(x, self.weight):
+        if not self.softcap and ops.head_pick_fusable(x, self.weight):
             return ops.head_pick(x, self.weight, temperature, seeds, positions, out=out)
         return super().pick(x, temperature, seeds, positions, out=out)
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "normed_token_embedding", NormedTokenEmbedding)
 register_part("head", "linear_head", LinearHead)

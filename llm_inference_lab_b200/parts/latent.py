@@ -1,0 +1,86 @@
+"""Attention whose keys and values are read from a cached low-rank latent."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from .base import CacheView, Mixer, StepContext, register_part
+from .spec import PagedLatent, PartSpec, TensorSpec
+
+
+class LatentAttention(Mixer):
+    """Queries through a latent: c_q = rmsnorm(W_dq h), q = W_uq c_q, per head [dim plain ; rot_dim rotated].
+    Keys and values through another: W_dkv h gives kv_rank numbers, RMS-normed into the latent c, and
+    rot_dim more, rotated, one key part shared by all heads.  Per head the plain key is W_uk c and the
+    value W_uv c; score = (q_plain . k_plain + q_rot . k_rot) * scale.  Only [c ; k_rot] is cached, one
+    vector per position for all heads (`PagedLatent`).
+
+    The key projection is absorbed into the query (q_lat = W_uk^T q_plain, so q_plain . W_uk c = q_lat . c)
+    and the value projection applied after the weighted sum of latents, so every step reads the cache as it
+    is, for prompts' portions and decoded tokens alike.  Parameters: `window` (0: all keys; else a query at
+    p sees the keys j with 0 <= p - j < window), `sink` (a learned number per head that joins the softmax's
+    denominator, unscaled, without key or value), rotary base and the number of rotated entries `rot_dims`
+    of the rotated part (entry i pairs with i + rot_dims / 2), `scale`."""
+
+    @classmethod
+    def tensors(cls, spec: PartSpec):
+        h, H, D, R, V = spec["hidden"], spec["heads"], spec["dim"], spec["rot_dim"], spec["vdim"]
+        Q, C, p = spec["q_rank"], spec["kv_rank"], spec.prefix
+        out = [TensorSpec(p + "dq", (Q, h)), TensorSpec(p + "dq.norm", (Q,), init="norm"),
+               TensorSpec(p + "uq", (H * (D + R), Q)), TensorSpec(p + "dkv", (C + R, h)),
+               TensorSpec(p + "dkv.norm", (C,), init="norm"), TensorSpec(p + "uk", (H * D, C)),
+               TensorSpec(p + "uv", (H * V, C)), TensorSpec(p + "o", (h, H * V))]
+        if spec.get("sink"):
+            out.append(TensorSpec(p + "sink", (H,), init="bias"))
+        return out
+
+    @classmethod
+    def cache_need(cls, spec: PartSpec):
+        return PagedLatent(spec["kv_rank"] + spec["rot_dim"], int(spec.get("window") or 0))
+
+    def __init__(self, spec, weights, dtype, device):
+        super().__init__(spec, weights, dtype, device)
+        self.heads, self.dim, self.rot_dim, self.vdim = (int(spec[k]) for k in ("heads", "dim", "rot_dim", "vdim"))
+        self.q_rank, self.kv_rank = int(spec["q_rank"]), int(spec["kv_rank"])
+        self.window, self.scale, self.eps = int(spec.get("window") or 0), float(spec["scale"]), float(spec["eps"])
+        self.rot_dims = int(spec.get("rot_dims", self.rot_dim))
+        if self.rot_dims % 2 or self.rot_dims > self.rot_dim:
+            raise ValueError("latent_attention: rot_dims must be even and at most rot_dim")
+        w = lambda n: self._weight(weights, n)  # noqa: E731
+        self.w_down = torch.cat([w("dq"), w("dkv")], dim=0).contiguous()
+        self.norm_q, self.norm_c = w("dq.norm"), w("dkv.norm")
+        self.w_uq = w("uq").contiguous()
+        H, D, C, V = self.heads, self.dim, self.kv_rank, self.vdim
+        # per head: the key projection transposed (it meets the query), the value projection as stored
+        self.w_uk_t = w("uk").view(H, D, C).transpose(1, 2).contiguous()      # [H, C, D]
+        self.w_uv = w("uv").view(H, V, C).contiguous()                        # [H, V, C]
+        self.w_o = w("o").contiguous()
+        self.sink = weights[spec.prefix + "sink"].to(torch.float32).contiguous() if spec.get("sink") else None
+        i = np.arange(self.rot_dims // 2, dtype=np.float64)
+        inv = np.power(float(spec["rot_base"]), -2.0 * i / max(self.rot_dims, 1)).astype(np.float32)
+        self.inv_freq = torch.from_numpy(inv).to(device)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        group = ctx.groups[cache.group]
+        H, D, R, C, V = self.heads, self.dim, self.rot_dim, self.kv_rank, self.vdim
+        T = x.shape[0]
+        proj = ops.linear(x, self.w_down, None, out_f32=True)
+        write = cache.write
+        cq = ops.latent_prep(proj, self.q_rank, C, R, self.norm_q, self.norm_c, ctx.row_pos, self.inv_freq,
+                             self.rot_dims, group.row_slot if write else None, cache.k if write else None, self.eps)
+        q = ops.linear(cq, self.w_uq, None)
+        q_cat = torch.empty((T, H, C + R), dtype=torch.float32, device=x.device)
+        ops.latent_q_rope(q, q_cat, H, D, R, C, ctx.row_pos, self.inv_freq, self.rot_dims)
+        q_heads = q.view(T, H, D + R)
+        for h in range(H):
+            ops.linear(q_heads[:, h, :D], self.w_uk_t[h], None, out_f32=True, out=q_cat[:, h, :C])
+        mixed = ops.latent_attention(q_cat, cache.k, self.sink, ctx, group, H, C, self.window, self.scale)
+        attn = torch.empty((T, H * V), dtype=self.dtype, device=x.device)
+        mixed_heads, attn_heads = mixed.view(T, H, C), attn.view(T, H, V)
+        for h in range(H):
+            ops.linear(mixed_heads[:, h, :], self.w_uv[h], None, out=attn_heads[:, h, :])
+        return ops.linear(attn, self.w_o, None, out_f32=True, allow_partial=True)
+
+
+register_part("mixer", "latent_attention", LatentAttention)

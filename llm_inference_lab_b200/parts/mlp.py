@@ -15,24 +15,33 @@ class GatedMLP(FeedForward):
     the epilogue of their matrix product."""
 
     ACTS = ("silu",)
+    NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+
+    @classmethod
+    def names(cls, spec: PartSpec) -> dict:
+        """Tensor names after the prefix; a model whose checkpoint calls them otherwise says so in `names`."""
+        return {**cls.NAMES, **(spec.get("names") or {})}
 
     @classmethod
     def tensors(cls, spec: PartSpec):
-        h, i, p = spec["hidden"], spec["intermediate"], spec.prefix
-        return [TensorSpec(p + "gate_proj.weight", (i, h)), TensorSpec(p + "up_proj.weight", (i, h)),
-                TensorSpec(p + "down_proj.weight", (h, i))]
+        h, i, p, n = spec["hidden"], spec["intermediate"], spec.prefix, cls.names(spec)
+        return [TensorSpec(p + n["gate"], (i, h)), TensorSpec(p + n["up"], (i, h)), TensorSpec(p + n["down"], (h, i))]
 
     def __init__(self, spec, weights, dtype, device):
         super().__init__(spec, weights, dtype, device)
         if spec["act"] not in self.ACTS:
             raise ValueError(f"gated_mlp: activation {spec['act']!r} is not built (known: {self.ACTS})")
-        self.w_gate_up = torch.cat([self._weight(weights, "gate_proj.weight"),
-                                    self._weight(weights, "up_proj.weight")], dim=0).contiguous()
-        self.w_down = self._weight(weights, "down_proj.weight").contiguous()
+        n = self.names(spec)
+        self.w_gate_up = torch.cat([self._weight(weights, n["gate"]), self._weight(weights, n["up"])],
+                                   dim=0).contiguous()
+        self.w_down = self._weight(weights, n["down"]).contiguous()
+        # True: the product leaves in 32-bit (whole, or as split-K partial sums), for a block whose
+        # residual stream is 32-bit
+        self.out_f32 = bool(spec.get("out_f32"))
 
     def forward(self, x, ctx):
         act = ops.linear_gated(x, self.w_gate_up)
-        return ops.linear(act, self.w_down, None, allow_partial=True)
+        return ops.linear(act, self.w_down, None, out_f32=self.out_f32, allow_partial=True)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

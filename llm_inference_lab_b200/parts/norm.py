@@ -27,4 +27,29 @@ class RMSNorm(Norm):
         return ops.add_rmsnorm(x, self.weight, self.eps, delta=delta, rows=rows)
 
 
+class StreamRMSNorm(Norm):
+    """RMS norm that reads a residual stream kept in 32-bit: y = x / sqrt(mean(x^2) + eps) * (offset + w),
+    rounded to the storage type at the end.  `offset` 1 serves weights stored around zero, 0 plain ones."""
+
+    @classmethod
+    def tensors(cls, spec: PartSpec):
+        return [TensorSpec(spec.prefix + spec.get("name", "weight"), (spec["hidden"],),
+                           init="around_zero" if spec.get("offset") else "norm")]
+
+    def __init__(self, spec, weights, dtype, device):
+        super().__init__(spec, weights, dtype, device)
+        self.weight = self._weight(weights, spec.get("name", "weight"))
+        self.eps = float(spec["eps"])
+        self.offset = float(spec.get("offset") or 0.0)
+
+    def forward(self, x, rows=None):
+        return ops.norm_stream(x, self.eps, self.offset, weight=self.weight, rows=rows)[1]
+
+    def forward_add(self, x, delta, rows=None):
+        if delta is not None:
+            raise ValueError("a 32-bit stream takes its sums in the block, not in the next norm")
+        return self.forward(x, rows)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "rmsnorm_stream", StreamRMSNorm)

@@ -19,7 +19,7 @@ class TensorSpec:
     """One tensor a part wants from the checkpoint."""
     name: str                 # full tensor name in the safetensors file
     shape: tuple[int, ...]
-    init: str = "matrix"      # random-weights mode: "matrix" | "bias" | "norm" | "table"
+    init: str = "matrix"      # random-weights mode: "matrix" | "bias" | "norm" | "table" | "around_zero" | "fraction"
     keep_f32: bool = False    # kept in 32-bit even in a bfloat16 engine
 
 
@@ -42,9 +42,10 @@ class LayerSpec:
     """One layer: a block arrangement around a mixer and a feed-forward."""
     block: str                     # arrangement kind, e.g. "prenorm"
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: Optional[PartSpec]        # None: a layer without a feed-forward (arrangements that allow it)
     norms: tuple[PartSpec, ...]    # as many as the arrangement wants
     hidden: int = 0
+    block_spec: Optional[PartSpec] = None   # constants and tensors of the arrangement itself, if it has any
 
 
 @dataclasses.dataclass(frozen=True)
@@ -62,6 +63,14 @@ class LayerCall:
 
 
 @dataclasses.dataclass(frozen=True)
+class Reentry:
+    """Something done to the residual stream right before the layer call ``before`` of the run order
+    (e.g. mixing the embedding output back in at the start of a pass over looped layers)."""
+    before: int
+    part: PartSpec
+
+
+@dataclasses.dataclass(frozen=True)
 class ModelBlueprint:
     hidden: int
     vocab: int
@@ -72,6 +81,10 @@ class ModelBlueprint:
     head: PartSpec
     max_positions: int
     eos_token_ids: tuple[int, ...] = ()
+    reentries: tuple[Reentry, ...] = ()
+    # True: the residual stream is kept in 32-bit floats whatever the engine's storage type; the
+    # embedding then hands out a 32-bit stream and the blocks add to it in 32-bit.
+    stream_f32: bool = False
 
 
 # ----------------------------------------------------------------------------------------
@@ -91,6 +104,18 @@ class PagedKV:
 
 
 @dataclasses.dataclass(frozen=True)
+class PagedLatent:
+    """One vector of ``width`` numbers per position, shared by all heads (a compressed key/value),
+    for every position (window == 0) or for the last ``window`` ones.  Lives in pages like `PagedKV`
+    and shares its block tables with every other paged cache of the same window."""
+    width: int
+    window: int = 0
+
+    def group_key(self):
+        return ("paged_kv", self.window)
+
+
+@dataclasses.dataclass(frozen=True)
 class FixedState:
     """A state of fixed size per request (recurrent mixers), kept in 32-bit."""
     shape: tuple[int, ...]
@@ -99,4 +124,4 @@ class FixedState:
         return ("fixed_state",)
 
 
-CacheNeed = Optional[PagedKV | FixedState]
+CacheNeed = Optional[PagedKV | PagedLatent | FixedState]

@@ -1,6 +1,7 @@
 """One registry from an architecture's name to its model.
 
-``config.json`` names its architecture in ``architectures[0]``; the registry
+``config.json`` names its architecture in ``architectures[0]`` (or in one string,
+``architecture``); the registry
 maps that name to a typed configuration class and to the function that turns
 the configuration into a `ModelBlueprint`.  The reference has no registry (its
 engine type is picked at compile time, rust/engine/examples/qwen2.rs:78-83);
@@ -43,6 +44,11 @@ def resolve(raw_config: dict) -> Architecture:
         if names[0] in _ARCHITECTURES:
             return _ARCHITECTURES[names[0]]
         raise ConfigError(f"architecture {names[0]!r} is not registered; known: {', '.join(architectures())}")
+    name = raw_config.get("architecture")       # some families name themselves in one string
+    if isinstance(name, str):
+        if name in _ARCHITECTURES:
+            return _ARCHITECTURES[name]
+        raise ConfigError(f"architecture {name!r} is not registered; known: {', '.join(architectures())}")
     model_type = raw_config.get("model_type")
     for arch in _ARCHITECTURES.values():
         if model_type in arch.model_types:
@@ -60,6 +66,8 @@ def load_config(model_dir: str) -> tuple[Architecture, ModelConfig]:
 def _register_builtin() -> None:
     from .config.qwen2 import Qwen2Config, qwen2_blueprint
     register_architecture("Qwen2ForCausalLM", Qwen2Config, qwen2_blueprint, model_types=("qwen2",))
+    from .config.sogulix import SogulixConfig, sogulix_blueprint
+    register_architecture("Sogulix", SogulixConfig, sogulix_blueprint)
 
 
 _register_builtin()

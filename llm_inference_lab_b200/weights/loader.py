@@ -57,8 +57,11 @@ def check_folder(files: ModelFiles, specs: Sequence[TensorSpec], model_dir: str,
     present = set(files.names())
     missing = sorted(n for n in wanted if n not in present)
     unexpected = sorted(n for n in present if n not in wanted and n not in optional)
+    def fits(got, want):     # a wanted extent of -1 is read from the file
+        return len(got) == len(want) and all(w == -1 or g == w for g, w in zip(got, want))
+
     wrong = [(n, files.shape(n), wanted[n].shape) for n in sorted(wanted)
-             if n in present and tuple(files.shape(n)) != tuple(wanted[n].shape)]
+             if n in present and not fits(tuple(files.shape(n)), tuple(wanted[n].shape))]
     if missing or unexpected or wrong:
         raise WeightsError(model_dir, missing, unexpected, wrong)
 

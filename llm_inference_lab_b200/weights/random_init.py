@@ -22,9 +22,15 @@ from .safetensors_io import save_file
 
 def random_tensor(spec: TensorSpec, seed: int, std: float, norm_std: float, scales: dict[str, float]) -> torch.Tensor:
     rng = np.random.default_rng([seed & 0xFFFFFFFF, zlib.crc32(spec.name.encode())])
+    if any(n < 0 for n in spec.shape):
+        raise ValueError(f"tensor {spec.name!r} has an extent that only a checkpoint gives; name it in the configuration")
+    if spec.init == "fraction":          # per-channel mixing weights in (0, 1)
+        return torch.from_numpy(rng.random(size=spec.shape, dtype=np.float32))
     values = rng.standard_normal(size=spec.shape, dtype=np.float32)
     # in place: a model of billions of values is made of tensors of hundreds of megabytes
-    if spec.init == "norm":
+    if spec.init == "around_zero":       # norm weights stored around zero (the gain is 1 + w)
+        values *= np.float32(norm_std)
+    elif spec.init == "norm":
         values *= np.float32(norm_std)
         values += np.float32(1.0)
     else:
