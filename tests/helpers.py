@@ -289,7 +289,8 @@ def run_trace_program(folder, dtype, steps, out_dir, max_tokens, page_size=None,
     done = [line for line in proc.stdout.splitlines() if line.startswith("done ")]
     assert [int(d.split()[1]) for d in done] == [s["step"] for s in steps], "a 'done' line per step, in order"
     with open(os.path.join(folder, "config.json")) as fh:
-        vocab = json.load(fh)["vocab_size"]
+        raw = json.load(fh)
+        vocab = raw["vocab_size"] if "vocab_size" in raw else raw["vocab"]
     out = {}
     at = {}
     for st in steps:

@@ -139,7 +139,7 @@ def latent_attention(h, w, p, mixer, eps):
     k_rot = rotate_half_pairs(k_rot, pos, base, dims)
     k_flat = (c @ w[p + "uk"].T).reshape(T, H, D)
     val = (c @ w[p + "uv"].T).reshape(T, H, V)
-    window = mixer["mask"]["size"]
+    window = mixer["mask"]["size"] if mixer.get("mask") else T      # no mask entry: every earlier token is seen
     out = np.zeros((T, H, V))
     for n in range(H):
         s = (q_flat[:, n] @ k_flat[:, n].T + q_rot[:, n] @ k_rot.T) * mixer["scale"]

@@ -1,0 +1,432 @@
+"""Sogulix on the GPU against the plain implementation (tests/plain_sogulix.py): each mechanism
+alone, then whole models under every way of cutting a trace, then generation through the scheduler."""
+import os
+
+import numpy as np
+import pytest
+
+import plain_sogulix as ps
+from helpers import (error_stats, make_model_folder, run_trace_inprocess, run_trace_program, tokens_needed,
+                     trace_mixed, trace_portions, trace_tail_decode, trace_whole)
+from sogulix_helpers import SMALL, SPREAD, config, delta, latent, plain_logits, sequences
+
+pytestmark = pytest.mark.gpu
+
+F32_MAX = 2e-4      # largest error over the largest logit, 32-bit engine against the 64-bit plain model
+BF16_MAX, BF16_RMS = 0.10, 0.04
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def make_ctx(q_lens, pos0, slots, page_size=4, num_pages=64, shuffle=None, dtype=None):
+    """A step's context made by hand: request r brings q_lens[r] rows from position pos0[r]; its pages are
+    taken from `shuffle` (a permutation of the pool), so that logical and physical order differ."""
+    torch = _torch()
+    from llm_inference_lab_b200.parts.base import GroupView, StepContext
+    dev = torch.device("cuda:0")
+    B, T = len(q_lens), sum(q_lens)
+    kv = [p + n for p, n in zip(pos0, q_lens)]
+    width = max(-(-k // page_size) for k in kv)
+    order = list(shuffle) if shuffle is not None else list(range(num_pages))
+    table = -np.ones((B, width), dtype=np.int32)
+    at = 0
+    for r in range(B):
+        for b in range(-(-kv[r] // page_size)):
+            table[r, b] = order[at]
+            at += 1
+    row_req = np.concatenate([np.full(n, r, dtype=np.int32) for r, n in enumerate(q_lens)])
+    row_pos = np.concatenate([np.arange(p, p + n, dtype=np.int32) for p, n in zip(pos0, q_lens)])
+    row_slot = np.array([table[r, p // page_size] * page_size + p % page_size for r, p in zip(row_req, row_pos)],
+                        dtype=np.int32)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)  # noqa: E731
+    group = GroupView(page_size, 0, t(row_slot), t(table))
+    ctx = StepContext(dtype=dtype or torch.float32, device=dev, n_tokens=T, n_requests=B,
+                      token_ids=t(np.zeros(T)), row_req=t(row_req), row_pos=t(row_pos),
+                      q_start=t(np.concatenate([[0], np.cumsum(q_lens)])), kv_len=t(kv), pos0=t(pos0),
+                      state_slot=t(slots), groups=[group], q_lens=list(q_lens), kv_lens=kv, state_slots=list(slots),
+                      max_q_len=max(q_lens), max_kv_len=max(kv))
+    return ctx, table
+
+
+# ---------------------------------------------------------------------------------------------
+# mechanisms alone
+# ---------------------------------------------------------------------------------------------
+def test_stream_operators_against_numpy():
+    torch = _torch()
+    from llm_inference_lab_b200.kernels import ops
+    rng = np.random.default_rng(0)
+    T, H, V = 11, 52, 30
+    dev = "cuda:0"
+    for dtype in (torch.float32, torch.bfloat16):
+        table = torch.from_numpy(rng.standard_normal((V, H)).astype(np.float32)).to(dev).to(dtype)
+        w1 = torch.from_numpy((0.2 * rng.standard_normal(H)).astype(np.float32)).to(dev).to(dtype)
+        w2 = torch.from_numpy((0.2 * rng.standard_normal(H)).astype(np.float32)).to(dev).to(dtype)
+        ids = torch.from_numpy(rng.integers(0, V, size=T).astype(np.int32)).to(dev)
+        x = ops.embed_norm(ids, table, w1, 1e-5, 1.0)
+        want = ps.norm_around_zero(table.double().cpu().numpy()[ids.cpu().numpy()], w1.double().cpu().numpy(), 1e-5)
+        assert x.dtype == torch.float32 and np.abs(x.cpu().numpy() - want).max() < 1e-5
+        rows = torch.tensor([7, 0, 7, 3], dtype=torch.int32, device=dev)
+        a, b = ops.norm_stream(x, 1e-5, 1.0, weight_f32=w1, weight=w2)
+        _, c = ops.norm_stream(x, 1e-5, 0.0, weight=w2, rows=rows)
+        xd = x.double().cpu().numpy()
+        tol = 1e-5 if dtype == torch.float32 else 2e-2
+        assert np.abs(a.cpu().numpy() - ps.norm_around_zero(xd, w1.double().cpu().numpy(), 1e-5)).max() < 1e-5
+        assert np.abs(b.double().cpu().numpy() - ps.norm_around_zero(xd, w2.double().cpu().numpy(), 1e-5)).max() < tol
+        assert np.abs(c.double().cpu().numpy()
+                      - ps.norm_plain_weight(xd[[7, 0, 7, 3]], w2.double().cpu().numpy(), 1e-5)).max() < tol
+        # the block's sum: whole products and split-K partial products
+        pa = torch.from_numpy(rng.standard_normal((3, T, H)).astype(np.float32)).to(dev)
+        pb = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).to(dev)
+        y = x.clone()
+        ops.stream_add(y, pa, w1, pb, w2, 0.3)
+        want = xd + 0.3 * (pa.double().cpu().numpy().sum(0) * w1.double().cpu().numpy()
+                           + pb.double().cpu().numpy() * w2.double().cpu().numpy())
+        assert np.abs(y.cpu().numpy() - want).max() < 1e-5
+        y = x.clone()
+        ops.stream_add(y, pb, w2, None, None, 2.0)
+        assert np.abs(y.cpu().numpy() - (xd + 2.0 * pb.double().cpu().numpy() * w2.double().cpu().numpy())).max() < 1e-5
+        both = ops.stream_concat(x, y, dtype)
+        assert both.shape == (T, 2 * H)
+        assert torch.equal(both[:, :H], x.to(dtype)) and torch.equal(both[:, H:], y.to(dtype))
+    logits = torch.from_numpy((20 * rng.standard_normal((5, 33))).astype(np.float32)).to(dev)
+    want = 7.0 * np.tanh(logits.double().cpu().numpy() / 7.0)
+    assert np.abs(ops.softcap(logits, 7.0).cpu().numpy() - want).max() < 1e-5
+
+
+def test_token_shift_keeps_each_request_s_last_row():
+    """Portions of three requests in one step, then single tokens: the row before a portion's first row is
+    the request's kept one, zeros at position 0, and slots do not leak into one another."""
+    torch = _torch()
+    from llm_inference_lab_b200.kernels import ops
+    rng = np.random.default_rng(1)
+    H = 36
+    mix = rng.random(H)
+    full = {r: rng.standard_normal((9, H)) for r in range(3)}
+    want = {r: ps.token_shift(full[r], mix) for r in range(3)}
+    kept = torch.full((5, H), 77.0, device="cuda:0")       # stale rows of earlier requests
+    mix_t = torch.from_numpy(mix.astype(np.float32)).cuda()
+    slots = [4, 0, 2]
+    done = [0, 0, 0]
+    for q_lens in ([3, 1, 5], [1, 2, 1], [5, 6, 3]):
+        ctx, _ = make_ctx(q_lens, done, slots)
+        rows = np.concatenate([full[r][done[r]: done[r] + n] for r, n in enumerate(q_lens)])
+        out = ops.token_shift(torch.from_numpy(rows.astype(np.float32)).cuda(), mix_t, kept, ctx)
+        exp = np.concatenate([want[r][done[r]: done[r] + n] for r, n in enumerate(q_lens)])
+        assert np.abs(out.cpu().numpy() - exp).max() < 1e-6
+        done = [d + n for d, n in zip(done, q_lens)]
+    assert torch.all(kept[1] == 77.0) and torch.all(kept[3] == 77.0)
+
+
+@pytest.mark.parametrize("heads,dim", [(2, 16), (3, 24), (1, 64)])
+def test_delta_rule_part_against_plain(heads, dim):
+    """The mixer alone in 32-bit: a prompt in one step, the same in portions of changing size down to
+    single tokens, two requests side by side with state slots that were used before."""
+    torch = _torch()
+    from llm_inference_lab_b200.parts import CacheView, PartSpec, lookup
+    rng = np.random.default_rng(dim)
+    hidden, rank, T = 40, 8, 29
+    spec = PartSpec("general_delta", {"hidden": hidden, "heads": heads, "dim": dim, "eps": 1e-5, "decay_rank": rank},
+                    prefix="m.")
+    cls = lookup("mixer", "general_delta")
+    w64 = {}
+    for t in cls.tensors(spec):
+        scale = {"m.w0": 2.0, "m.a.b": 2.0, "m.norm": 1.0}.get(t.name, 0.3)
+        w64[t.name] = scale * rng.standard_normal(t.shape)
+    weights = {k: torch.from_numpy(v.astype(np.float32)).cuda() for k, v in w64.items()}
+    w64 = {k: v.astype(np.float32).astype(np.float64) for k, v in w64.items()}
+    part = cls(spec, weights, torch.float32, "cuda:0")
+    xs = [rng.standard_normal((T, hidden)), rng.standard_normal((T - 6, hidden))]
+    want = [ps.general_delta(x.astype(np.float32).astype(np.float64), w64, "m.", {"heads": heads, "dim": dim}, 1e-5)
+            for x in xs]
+    state = torch.full((4, heads, dim, dim), 5.0, device="cuda:0")
+    view = CacheView(cls.cache_need(spec), state=state)
+    for cuts in ([[T], [T - 6]], [[5, 1, 9, 2, 1, 1, 10], [1, 7, 8, 1, 2, 4]]):
+        state[1].zero_(), state[3].zero_()          # what the engine does for a request's first tokens
+        done, got = [0, 0], [[], []]
+        for step in range(max(len(c) for c in cuts)):
+            live = [r for r in range(2) if step < len(cuts[r])]
+            q_lens = [cuts[r][step] for r in live]
+            ctx, _ = make_ctx(q_lens, [done[r] for r in live], [[3, 1][r] for r in live])
+            x = np.concatenate([xs[r][done[r]: done[r] + n] for r, n in zip(live, q_lens)])
+            out = part.forward(torch.from_numpy(x.astype(np.float32)).cuda(), ctx, view)
+            out = out.sum(0) if out.dim() == 3 else out
+            at = 0
+            for r, n in zip(live, q_lens):
+                got[r].append(out[at: at + n].cpu().numpy())
+                at += n
+                done[r] += n
+        for r in range(2):
+            err = np.abs(np.concatenate(got[r]) - want[r]).max()
+            assert err < 2e-4 * max(1.0, np.abs(want[r]).max()), (cuts, r, err)
+    assert torch.all(state[0] == 5.0) and torch.all(state[2] == 5.0)
+
+
+def _latent_setup(heads, C, R, page_size, num_pages, dtype, rng):
+    torch = _torch()
+    cache = torch.from_numpy(rng.standard_normal((num_pages, page_size, C + R)).astype(np.float32)).cuda().to(dtype)
+    return cache, list(rng.permutation(num_pages))
+
+
+def _plain_latent_scores(q_cat, latents, sink, window, scale, positions, C):
+    """Softmax with a sink over [c ; kr] rows, by the definition: q_cat [rows, heads, C + R], latents
+    [keys, C + R] from position 0."""
+    out = np.zeros(q_cat.shape[:2] + (C,))
+    for i, p in enumerate(positions):
+        lo = max(0, p - window + 1) if window else 0
+        keys = latents[lo: p + 1]
+        for h in range(q_cat.shape[1]):
+            s = keys @ q_cat[i, h] * scale
+            m = max(s.max(), sink[h])
+            e = np.exp(s - m)
+            out[i, h] = (e / (e.sum() + np.exp(sink[h] - m))) @ keys[:, :C]
+    return out
+
+
+@pytest.mark.parametrize("window", [0, 13, 32])
+def test_latent_attention_kernel_random(window):
+    """Rows of prompts' portions and decoded tokens in one launch, pages in shuffled order, windows that
+    end inside pages and inside the kernel's tiles of keys."""
+    torch = _torch()
+    from llm_inference_lab_b200.kernels import ops
+    rng = np.random.default_rng(window)
+    H, C, R, page = 3, 20, 12, 4
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        cache, order = _latent_setup(H, C, R, page, 96, dtype, rng)
+        q_lens, pos0 = [37, 1, 9, 1], [30, 70, 0, 0]
+        ctx, table = make_ctx(q_lens, pos0, [0, 1, 2, 3], page, 96, order)
+        q_cat = torch.from_numpy(rng.standard_normal((sum(q_lens), H, C + R)).astype(np.float32)).cuda()
+        sink = torch.from_numpy(rng.standard_normal(H).astype(np.float32)).cuda()
+        out = ops.latent_attention(q_cat, cache, sink, ctx, ctx.groups[0], H, C, window, 0.3)
+        out = out.double().cpu().numpy().reshape(-1, H, C)
+        flat = cache.double().cpu().numpy().reshape(-1, C + R)
+        at = 0
+        for r, (n, p0) in enumerate(zip(q_lens, pos0)):
+            lat = np.stack([flat[table[r, p // page] * page + p % page] for p in range(p0 + n)])
+            want = _plain_latent_scores(q_cat[at: at + n].double().cpu().numpy(), lat, sink.double().cpu().numpy(),
+                                        window, 0.3, range(p0, p0 + n), C)
+            assert np.abs(out[at: at + n] - want).max() < tol, (dtype, r)
+            at += n
+
+
+@pytest.mark.parametrize("decode", [False, True])
+def test_latent_attention_window_edges_and_far_keys(decode):
+    """One key made to stand out (its latent and the query point the same way, scaled up): the row's output
+    is that key's latent while the key lies inside the window, down to its last place, and none of it one
+    place further; without a window a key hundreds of places back is found.  In prompts' portions and for
+    single decoded tokens, with the marked key at a page's border, a tile's border and elsewhere."""
+    torch = _torch()
+    from llm_inference_lab_b200.kernels import ops
+    rng = np.random.default_rng(5)
+    H, C, R, page, pages = 2, 16, 8, 8, 80
+    for window in (0, 24, 33):
+        for key_at in (0, 7, 8, 31, 32, 63, 64, 100, 317):
+            cache, order = _latent_setup(H, C, R, page, pages, torch.float32, rng)
+            cache *= 0.05
+            n_keys = 420
+            ctx_all, table = make_ctx([n_keys], [0], [0], page, pages, order)
+            slot = table[0, key_at // page] * page + key_at % page
+            mark = np.zeros(C + R, dtype=np.float32)
+            mark[3] = 6.0
+            cache.view(-1, C + R)[slot] = torch.from_numpy(mark).cuda()
+            probes = sorted({p for p in (key_at, key_at + 1, key_at + window - 1, key_at + window, key_at + window + 1,
+                                         n_keys - 1) if key_at <= p < n_keys})
+            for p in probes:
+                if decode:
+                    ctx, _ = make_ctx([1], [p], [0], page, pages, order)
+                    rows = [p]
+                else:
+                    first = max(0, p - 10)
+                    ctx, _ = make_ctx([p + 1 - first], [first], [0], page, pages, order)
+                    rows = list(range(first, p + 1))
+                q_cat = torch.zeros((len(rows), H, C + R), device="cuda:0")
+                q_cat[:, :, 3] = 6.0
+                out = ops.latent_attention(q_cat, cache, torch.full((H,), -30.0, device="cuda:0"), ctx, ctx.groups[0],
+                                           H, C, window, 1.0).view(len(rows), H, C)
+                for i, pos in enumerate(rows):
+                    if pos < key_at:
+                        continue
+                    inside = window == 0 or pos - key_at < window
+                    got = out[i, :, 3].cpu().numpy()
+                    assert (np.all(got > 5.9) if inside else np.all(got < 1.0)), (window, key_at, pos, got)
+
+
+def test_latent_attention_sink_only_joins_the_denominator():
+    torch = _torch()
+    from llm_inference_lab_b200.kernels import ops
+    rng = np.random.default_rng(9)
+    H, C, R, page = 2, 8, 8, 4
+    cache, order = _latent_setup(H, C, R, page, 16, torch.float32, rng)
+    ctx, _ = make_ctx([6], [0], [0], page, 16, order)
+    q_cat = torch.from_numpy(rng.standard_normal((6, H, C + R)).astype(np.float32)).cuda()
+    free = ops.latent_attention(q_cat, cache, None, ctx, ctx.groups[0], H, C, 0, 0.5)
+    low = ops.latent_attention(q_cat, cache, torch.full((H,), -80.0, device="cuda:0"), ctx, ctx.groups[0], H, C, 0, 0.5)
+    assert (free - low).abs().max() < 1e-6
+    # the first row sees one key with weight 1: a sink s turns it into 1 / (1 + exp(s - score)), whatever
+    # the scale of the scores is (the sink itself is not scaled)
+    sink = torch.tensor([0.7, -1.1], device="cuda:0")
+    out = ops.latent_attention(q_cat, cache, sink, ctx, ctx.groups[0], H, C, 0, 0.5).view(6, H, C)
+    slot = int(ctx.groups[0].row_slot[0])
+    key = cache.view(-1, C + R)[slot]
+    for h in range(H):
+        score = float((q_cat[0, h] * key).sum()) * 0.5
+        weight = 1.0 / (1.0 + np.exp(float(sink[h]) - score))
+        assert (out[0, h] - weight * key[:C]).abs().max() < 1e-5
+
+
+# ---------------------------------------------------------------------------------------------
+# whole models under every cut
+# ---------------------------------------------------------------------------------------------
+def _engine(folder, dtype, opt, steps, **kw):
+    from llm_inference_lab_b200.engine import Engine
+    page = opt["page_size"]
+    unit = max(64, page)
+    pool = tokens_needed(steps, unit)
+    return Engine(folder, dtype, max_tokens=pool, page_size=page, max_requests=4, max_batch_tokens=max(pool, 64),
+                  max_seq_len=pool, **kw)
+
+
+def _check(got, want, dtype, label):
+    """32-bit: every position within F32_MAX.  bfloat16: the rms error over all positions within BF16_RMS
+    and all but one position in a hundred within BF16_MAX.  (A head's output is divided by its own root
+    mean square, so where a head's output is nearly zero, as it can be at a sequence's first tokens, its
+    sign hangs on the last bit of a bfloat16 product: such a position is ill-conditioned in the design
+    itself, and the 32-bit run of the same trace shows that no mechanism is at fault.)"""
+    worst, rms, where = error_stats(got, want)
+    if dtype == "float32":
+        assert worst < F32_MAX, (label, worst, where)
+        return
+    peak = max(float(np.abs(v).max()) for v in want.values())
+    over = [key for key, row in got.items() if np.abs(row - want[key[0]][key[1]]).max() > BF16_MAX * peak]
+    assert rms < BF16_RMS and len(over) <= max(1, len(got) // 100), (label, worst, rms, over[:5])
+
+
+ONE_LAYER = {
+    "delta": config([delta(2, 16, ff=None)], vocab=53, width=32),
+    "delta+ff": config([delta(3, 24, rank=4, ff=48)], vocab=53, width=32, loop=(0, 1, 2)),
+    "latent": config([latent(2, 16, 8, 16, 24, 16, window=19)], vocab=53, width=32),
+    "latent+ff": config([latent(4, 8, 16, 24, 16, 32, window=0, rot_dims=8, ff=48)], vocab=53, width=32, softcap=None),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(ONE_LAYER))
+def test_one_layer_models(tmp_path, name, dtype):
+    rng = np.random.default_rng(3)
+    cfg = ONE_LAYER[name]
+    folder = make_model_folder(str(tmp_path / "m"), cfg, 21, dtype, std=0.08, scales=SPREAD)
+    seqs = sequences(rng, cfg["vocab"], [45, 1, 30])
+    want = plain_logits(folder, seqs)
+    for label, steps in (("whole", trace_whole(seqs)), ("tail", trace_tail_decode(seqs, tail=25)),
+                         ("portions", trace_portions(seqs))):
+        eng = _engine(folder, dtype, dict(page_size=8), steps)
+        _check(run_trace_inprocess(eng, steps), want, dtype, (name, label))
+        assert eng.cache.live_requests == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(SMALL))
+def test_models_under_every_cut(tmp_path, name, dtype):
+    """Whole prompts; the tail decoded token by token, long enough for every window to pass over decoded
+    tokens; portions of 2 to 11 tokens; up to four live requests with portions beside single tokens, in a
+    pool so small that pages and state slots are used again."""
+    cfg, opt = SMALL[name]
+    rng = np.random.default_rng(opt["seed"])
+    folder = make_model_folder(str(tmp_path / "m"), cfg, opt["seed"], dtype, std=0.08, scales=SPREAD)
+    seqs = sequences(rng, cfg["vocab"], [150, 3, 61, 90, 1, 77, 40])
+    want = plain_logits(folder, seqs)
+    traces = {"whole": trace_whole(seqs), "tail": trace_tail_decode(seqs, tail=70), "portions": trace_portions(seqs),
+              "mixed": trace_mixed(seqs, np.random.default_rng(1), max_live=4)}
+    for label, steps in traces.items():
+        eng = _engine(folder, dtype, opt, steps)
+        got = run_trace_inprocess(eng, steps)
+        assert len(got) == sum(len(v) for v in seqs.values())
+        _check(got, want, dtype, (name, label))
+        assert eng.cache.live_requests == 0 and all(f == eng.num_pages for f in eng.free_pages())
+
+
+def test_cuts_agree_bit_for_bit_in_32_bit(tmp_path):
+    """In 32-bit no sum's order depends on how a prompt was cut or on what else is in the batch."""
+    cfg, opt = SMALL["A"]
+    folder = make_model_folder(str(tmp_path / "m"), cfg, 5, "float32", std=0.08, scales=SPREAD)
+    seqs = sequences(np.random.default_rng(2), cfg["vocab"], [70, 33, 9])
+    results = []
+    for steps in (trace_whole(seqs), trace_portions(seqs), trace_mixed(seqs, np.random.default_rng(3), max_live=3)):
+        results.append(run_trace_inprocess(_engine(folder, "float32", opt, steps), steps))
+    for other in results[1:]:
+        for key, row in results[0].items():
+            assert np.abs(row - other[key]).max() <= 1e-5, key
+
+
+def test_trace_program_and_a_failed_step(tmp_path):
+    """bin/trace_run on a Sogulix folder; and a step that fails leaves state and pages as they were."""
+    from llm_inference_lab_b200.engine import Entry
+    cfg, opt = SMALL["C"]
+    folder = make_model_folder(str(tmp_path / "m"), cfg, 8, "float32", std=0.08, scales=SPREAD)
+    seqs = sequences(np.random.default_rng(4), cfg["vocab"], [50, 20, 35, 8, 41])
+    want = plain_logits(folder, seqs)
+    steps = trace_mixed(seqs, np.random.default_rng(6), max_live=4)
+    out = str(tmp_path / "out")
+    os.makedirs(out)
+    got = run_trace_program(folder, "float32", steps, out, tokens_needed(steps, 64))
+    _check(got, want, "float32", "program")
+    ids = seqs["s0"]
+    eng = _engine(folder, "float32", opt, trace_whole(seqs))
+    eng.step([Entry(0, ids[:20], [])])
+    states = [t.clone() for t in eng.state_tensors]
+    with pytest.raises(Exception):
+        eng.step([Entry(0, ids[20:30], []), Entry(1, [cfg["vocab"] + 5], [0])])     # refused before it runs
+    try:
+        from llm_inference_lab_b200.kernels import ops
+        old = ops.softcap
+        ops.softcap = lambda *a, **k: (_ for _ in ()).throw(RuntimeError("injected"))   # fails after the layers ran
+        with pytest.raises(RuntimeError):
+            eng.step([Entry(0, ids[20:30], [9])])
+    finally:
+        ops.softcap = old
+    assert all(bool((a == b).all()) for a, b in zip(states, eng.state_tensors))
+    logits = eng.step([Entry(0, ids[20:], [len(ids) - 21])]).cpu().numpy()
+    assert np.abs(logits[0] - want["s0"][-1]).max() < F32_MAX * max(1.0, np.abs(want["s0"]).max())
+
+
+# ---------------------------------------------------------------------------------------------
+# generation through the scheduler
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_scheduler(tmp_path, name):
+    """More requests than state slots, prompts cut under a small token budget: greedy tokens in 32-bit
+    equal the plain model's."""
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.kernels import ops
+    from llm_inference_lab_b200.sampling import SamplingConfig
+    cfg, opt = SMALL[name]
+    folder = make_model_folder(str(tmp_path / "m"), cfg, 17, "float32", std=0.08, scales=SPREAD)
+    pcfg, w = ps.read_folder(folder)
+    rng = np.random.default_rng(7)
+    prompts = [[int(t) for t in rng.integers(0, cfg["vocab"], size=n)] for n in (5, 40, 1, 23, 12, 31)]
+    llm = LLM(folder, "float32", page_size=opt["page_size"], kv_tokens=512, max_requests=3, max_batch_tokens=24,
+              max_seq_len=128, device="cuda:0")
+    results = llm.generate(prompts, SamplingConfig(max_new_tokens=12, ignore_eos=True))
+    ops.take_device_errors()
+    for prompt, res in zip(prompts, results):
+        assert res.finish_reason == "length"
+        assert res.tokens == ps.greedy(pcfg, w, prompt, 12)
+    assert llm.engine.cache.live_requests == 0
+
+
+def test_command_line_generates(tmp_path):
+    import json
+    import subprocess
+    import sys
+    cfg, opt = SMALL["C"]
+    folder = make_model_folder(str(tmp_path / "m"), cfg, 19, "float32", std=0.08, scales=SPREAD)
+    pcfg, w = ps.read_folder(folder)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc = subprocess.run([sys.executable, "-m", "llm_inference_lab_b200.cli", "--model-dir", folder, "--dtype", "f32",
+                           "--prompt-ids", "3,14,15,9,2,6", "--max-new-tokens", "6", "--kv-tokens", "256"],
+                          cwd=root, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    line = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert line["generated_ids"] == ps.greedy(pcfg, w, [3, 14, 15, 9, 2, 6], 6)
