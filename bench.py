@@ -360,6 +360,228 @@ def run_serve(folder, cfg, layers, requests, chunk, new_tokens, max_seq, lo=128,
             "preemptions": sum(r.preemptions for r in results)}
 
 
+# ----------------------------------------------------------------------------------------
+# --arch sogulix: the Sogulix design beside Qwen2 at equal layer sizes (random weights)
+# ----------------------------------------------------------------------------------------
+SOGULIX_SHAPES = {
+    # width, feed-forward and vocabulary of the Qwen2.5 shape of the same name; mixers sized alike
+    "0.5B": dict(heads=14, dim=64, rot_dim=32, vdim=64, kv_rank=256, q_rank=384, window=1024, decay_rank=64),
+    "1.5B": dict(heads=12, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768, window=2048, decay_rank=96),
+}
+
+
+def sogulix_config(shape, layers):
+    q, m = SHAPES[shape], SOGULIX_SHAPES[shape]
+    mlp = {"kind": "dense", "ff": q["intermediate_size"]}
+    delta = {"type": "general_delta", "mlp": mlp,
+             "mixer": {"heads": m["heads"], "dim": m["dim"], "decay_rank": m["decay_rank"]}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": m["heads"], "dim": m["dim"], "rot_dim": m["rot_dim"], "vdim": m["vdim"],
+                        "kv_rank": m["kv_rank"], "q_rank": m["q_rank"], "mask": {"size": m["window"]},
+                        "rot": {"base": 10000.0, "dims": m["rot_dim"]}, "scale": (m["dim"] + m["rot_dim"]) ** -0.5}}
+    return {"architecture": "Sogulix", "vocab": q["vocab_size"], "width": q["hidden_size"], "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "logit_softcap": 30.0, "layers": [delta if i % 2 == 0 else latent for i in range(layers)]}
+
+
+def arch_folder(cfg_dict, tag):
+    import torch
+    from llm_inference_lab_b200.registry import resolve
+    from llm_inference_lab_b200.weights import write_random_model
+
+    folder = os.path.join(tempfile.gettempdir(), f"lab_b200_bench_{tag}_{os.getuid()}")
+    marker = os.path.join(folder, ".complete")
+    if not os.path.exists(marker):
+        cfg = resolve(cfg_dict).config_class.from_dict(cfg_dict)
+        write_random_model(cfg, folder, seed=0, dtype=torch.bfloat16, std=0.02, norm_std=0.0)
+        open(marker, "w").write("ok")
+    return folder
+
+
+def timed(fn, repeats=7, flush=None):
+    """Median milliseconds of fn() between CUDA events, after three warm-up calls; `flush` (a buffer
+    larger than L2) is overwritten before every timed call."""
+    import torch
+    times = []
+    for it in range(3 + repeats):
+        if flush is not None:
+            flush.add_(1)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= 3:
+            times.append(e0.elapsed_time(e1))
+    return statistics.median(times)
+
+
+def model_points(folder, batch, prompt_len, prefill_tokens, decode_steps):
+    """Prefill and eager decode throughput of a model folder through `Engine.step`."""
+    import numpy as np
+    import torch
+    from llm_inference_lab_b200.engine import Engine, Entry
+    from llm_inference_lab_b200.kernels import ops
+
+    rng = np.random.default_rng(0)
+    engine = Engine(folder, "bf16", max_tokens=batch * (prompt_len + 256) + prefill_tokens + 64, page_size=PAGE_SIZE,
+                    max_requests=batch + 1, max_batch_tokens=max(prefill_tokens, prompt_len), max_seq_len=4096)
+    out = {}
+    prompt = [int(t) for t in rng.integers(0, engine.vocab, prefill_tokens)]
+
+    def prefill():
+        engine.step([Entry(999, prompt, [prefill_tokens - 1])])
+        engine.close(999)
+
+    launches0 = ops.COUNTER.launches
+    prefill()
+    out["prefill_launches"] = ops.COUNTER.launches - launches0
+    ms = timed(prefill, repeats=5)
+    out["prefill_ms"], out["prefill_tok_s"] = round(ms, 3), round(prefill_tokens / (ms / 1e3), 1)
+    for r in range(batch):
+        engine.step([Entry(r, [int(t) for t in rng.integers(0, engine.vocab, prompt_len)], [])])
+    entries = [Entry(r, [7 + r], [0]) for r in range(batch)]
+    launches0 = ops.COUNTER.launches
+    engine.step(entries)
+    out["decode_launches"] = ops.COUNTER.launches - launches0
+
+    def decode():
+        for _ in range(decode_steps):
+            engine.step(entries)
+
+    ms = timed(decode, repeats=3) / decode_steps
+    out["decode_ms_per_step"], out["decode_tok_s"] = round(ms, 4), round(batch / (ms / 1e3), 1)
+    ops.take_device_errors()
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
+def bench_ctx(q_lens, pos0, page_size, device):
+    """A step's context with pages in order, for timing single kernels."""
+    import numpy as np
+    import torch
+    from llm_inference_lab_b200.parts.base import GroupView, StepContext
+
+    kv = [p + n for p, n in zip(pos0, q_lens)]
+    blocks = [-(-k // page_size) for k in kv]
+    width = (max(blocks) + 7) & ~7
+    table = -np.ones((len(q_lens), width), dtype=np.int32)
+    at = 0
+    for r, b in enumerate(blocks):
+        table[r, :b] = np.arange(at, at + b)
+        at += b
+    row_req = np.concatenate([np.full(n, r) for r, n in enumerate(q_lens)])
+    row_pos = np.concatenate([np.arange(p, p + n) for p, n in zip(pos0, q_lens)])
+    row_slot = table[row_req, row_pos // page_size] * page_size + row_pos % page_size
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(device)  # noqa: E731
+    group = GroupView(page_size, 0, t(row_slot), t(table))
+    ctx = StepContext(dtype=torch.bfloat16, device=device, n_tokens=sum(q_lens), n_requests=len(q_lens),
+                      token_ids=t(np.zeros(sum(q_lens))), row_req=t(row_req), row_pos=t(row_pos),
+                      q_start=t(np.concatenate([[0], np.cumsum(q_lens)])), kv_len=t(kv), pos0=t(pos0),
+                      state_slot=t(np.arange(len(q_lens))), groups=[group], q_lens=list(q_lens), kv_lens=kv,
+                      state_slots=list(range(len(q_lens))), max_q_len=max(q_lens), max_kv_len=max(kv))
+    return ctx, at
+
+
+def kernel_points(shape, batch, ctx_len, prefill_tokens, pk):
+    """The new design's own kernels and Qwen2's like kernels at the shape's sizes, each alone between
+    CUDA events with L2 flushed: milliseconds, and the fraction of the roofline (measured copy bandwidth
+    for kernels that stream, measured bf16 product rate for the attention kernels of a prompt)."""
+    import torch
+    from llm_inference_lab_b200.kernels import ops
+
+    dev = torch.device("cuda:0")
+    q, m = SHAPES[shape], SOGULIX_SHAPES[shape]
+    width, H, D, R, C, V = q["hidden_size"], m["heads"], m["dim"], m["rot_dim"], m["kv_rank"], m["vdim"]
+    hd = H * D
+    flush = torch.zeros((160 << 20,), dtype=torch.int16, device=dev)
+    bw, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    rows = {}
+
+    def record(name, ms, nbytes=None, flops=None):
+        entry = {"ms": round(ms, 4)}
+        if nbytes is not None:
+            entry.update(gbs=round(nbytes / (ms / 1e3) / 1e9, 1), frac_hbm=round(nbytes / (ms / 1e3) / bw, 4))
+        if flops is not None:
+            entry.update(tflops=round(flops / (ms / 1e3) / 1e12, 2), frac_bf16=round(flops / (ms / 1e3) / tf, 4))
+        rows[name] = entry
+
+    bf = lambda *s: torch.randn(*s, device=dev).to(torch.bfloat16)  # noqa: E731
+    for label, q_lens, pos0 in (("prefill", [prefill_tokens], [0]), ("decode", [1] * batch, [ctx_len] * batch)):
+        T, B = sum(q_lens), len(q_lens)
+        ctx, pages = bench_ctx(q_lens, pos0, PAGE_SIZE, dev)
+        # generalized delta rule: reads five 32-bit projections and the decay's, the state in and out
+        proj, dpre = torch.randn(T, 5 * hd + 64, device=dev), torch.randn(T, hd, device=dev)
+        state = torch.zeros(B, H, D, D, device=dev)
+        ones = bf(hd)
+        ms = timed(lambda: ops.delta_rule(proj, dpre, ones, ones, ones, state, ctx, H, D, 1e-6, 0.6), flush=flush)
+        record(f"delta_rule {label}", ms, nbytes=T * hd * (6 * 4 + 2) + 2 * state.numel() * 4,
+               flops=None if label == "decode" else 8.0 * T * H * D * D)
+        # latent attention: reads the window's latents once per request (decode) or the scores' and the
+        # weighted sums' arithmetic (prompt)
+        W = C + R
+        cache = bf(pages, PAGE_SIZE, W)
+        q_cat = torch.randn(T, H, W, device=dev)
+        sink = torch.zeros(H, device=dev)
+        ms = timed(lambda: ops.latent_attention(q_cat, cache, sink, ctx, ctx.groups[0], H, C, m["window"], 0.1),
+                   flush=flush)
+        keys = [min(m["window"], p + n) for p, n in zip(pos0, q_lens)]
+        pairs = sum(sum(min(m["window"], p + i + 1) for i in range(n)) for p, n in zip(pos0, q_lens))
+        record(f"latent_attention {label}", ms, nbytes=sum(keys) * W * 2 + T * H * (W * 4 + C * 2),
+               flops=2.0 * pairs * H * (W + C))
+        # Qwen2's attention at the same heads (grouped 7:1 as in the shape) and head size
+        nq, nkv = q["num_attention_heads"], q["num_key_value_heads"]
+        d = q["hidden_size"] // nq
+        if ops.attention_tc_supported(d):
+            ck, cv = bf(pages, nkv, PAGE_SIZE, d), bf(pages, nkv, PAGE_SIZE, d)
+            qq = bf(T, nq * d)
+            ms = timed(lambda: ops.attention_tc(qq, ck, cv, ctx.q_start, ctx.kv_len, ctx.pos0, ctx.groups[0].block_table,
+                                                B, ctx.q_lens, ctx.max_kv_len, nq, nkv, d, 0, d ** -0.5), flush=flush)
+            all_pairs = sum(sum(p + i + 1 for i in range(n)) for p, n in zip(pos0, q_lens))
+            record(f"qwen2 attention {label}", ms, nbytes=sum(p + n for p, n in zip(pos0, q_lens)) * 2 * nkv * d * 2
+                   + 2 * T * nq * d * 2, flops=4.0 * all_pairs * nq * d)
+        # the row-wise operators around a block
+        x = torch.randn(T, width, device=dev)
+        w1 = bf(width)
+        kept = torch.zeros(B, width, device=dev)
+
+        def norms():
+            n, _ = ops.norm_stream(x, 1e-6, 1.0, weight_f32=w1, weight=w1)
+            ops.token_shift(n, w1, kept, ctx)
+
+        ms = timed(norms, flush=flush)
+        record(f"two norms + token shift {label}", ms, nbytes=T * width * (4 + 4 + 2 + 4 + 2))
+        a, f = torch.randn(T, width, device=dev), torch.randn(T, width, device=dev)
+        ms = timed(lambda: ops.stream_add(x, a, w1, f, w1, 0.5), flush=flush)
+        record(f"stream add {label}", ms, nbytes=T * width * 16)
+        xb, delta = bf(T, width), bf(T, width)
+        ms = timed(lambda: ops.add_rmsnorm(xb, w1, 1e-6, delta=delta), flush=flush)
+        record(f"qwen2 add + norm {label}", ms, nbytes=T * width * 8)
+    ops.take_device_errors()
+    return rows
+
+
+def run_arch_sogulix(args):
+    shape, layers = args.shape, args.layers or 4
+    pk, pk_src = peaks()
+    qcfg = dict(SHAPES[shape], num_hidden_layers=layers)
+    folders = {"sogulix": arch_folder(sogulix_config(shape, layers), f"sogulix_{shape}_L{layers}"),
+               "qwen2": model_folder(SHAPES[shape], layers)}
+    clocks = ClockSampler()
+    with clocks:
+        models = {name: model_points(folder, args.batch, args.prompt_len, PREFILL_TOKENS, 20)
+                  for name, folder in folders.items()}
+        kernels = kernel_points(shape, args.batch, args.prompt_len + 512, PREFILL_TOKENS, pk)
+    print(json.dumps({
+        "arch": "sogulix", "beside": "qwen2", "shape": shape, "layers": layers, "batch": args.batch,
+        "prompt_len": args.prompt_len, "prefill_tokens": PREFILL_TOKENS, "dtype": "bf16", "mode": "eager launches",
+        "data": "synthetic: random weights N(0, 0.02) seed 0", "sogulix_mixers": SOGULIX_SHAPES[shape],
+        "hidden": qcfg["hidden_size"], "intermediate": qcfg["intermediate_size"], "vocab": qcfg["vocab_size"],
+        "models": models, "kernels": kernels, "peaks": dict(pk, source=pk_src), "clocks": clocks.summary()}))
+    return 0
+
+
 def kv_bytes_per_token(cfg, layers):
     d = cfg["hidden_size"] // cfg["num_attention_heads"]
     return 2 * layers * 2 * cfg["num_key_value_heads"] * d
@@ -388,6 +610,10 @@ def main() -> int:
     ap.add_argument("--stack-stamps", action="store_true",
                     help="run a few eager decode steps with the decode stack's in-kernel clock on and print what "
                          "each kind of phase took")
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "sogulix"],
+                    help="sogulix: instead of the headline run, prefill and decode throughput of the Sogulix design "
+                         "beside Qwen2 at the layer sizes of --shape (0.5B or 1.5B; --layers, default 4), and each "
+                         "of its kernels beside Qwen2's like kernel; prints its own line")
     ap.add_argument("--only-prefill", type=int, default=0, metavar="TOKENS",
                     help="run only a prefill of TOKENS tokens a few times and print its time (for profiling)")
     args = ap.parse_args()
@@ -414,6 +640,11 @@ def main() -> int:
     from llm_inference_lab_b200.engine import Engine
     from llm_inference_lab_b200.engine.decode_graph import DecodeGraphs
 
+    if args.arch == "sogulix":
+        if args.shape not in SOGULIX_SHAPES:
+            ap.error("--arch sogulix knows the shapes " + ", ".join(sorted(SOGULIX_SHAPES)))
+        args.layers = 0 if args.layers == cfg["num_hidden_layers"] else args.layers
+        return run_arch_sogulix(args)
     folder = model_folder(cfg, args.layers)
     pk, pk_src = peaks()
     if args.serve:

@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
     const __nv_bfloat16* __restrict__ cache_k, const __nv_bfloat16* __restrict__ cache_v,
     const int* __restrict__ q_start, const int* __restrict__ kv_len_arr, const int* __restrict__ pos0_arr,
     const int* __restrict__ block_table, int max_blocks, int n_q, int n_kv, int page_size, int num_pages, int window,
-    float scale_log2, int min_q_len) {
+    float scale_log2, int min_q_len, const float* __restrict__ sink) {
   extern __shared__ __align__(16) uint8_t smem[];
   pdl_trigger();
   pdl_wait();
@@ -81,6 +81,13 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
     lo[r] = window > 0 ? max(0, pos - window + 1) : 0;
   }
   float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  if (sink != nullptr) {
+    // A sink: a number per query head that joins the softmax's denominator as exp(sink), unscaled, with
+    // no key and no value.  It opens the running maximum (in the scores' log2 units) and the sum, once
+    // per row: a row's sum is spread over the four lanes that hold it.
+    m[0] = m[1] = sink[h] * LOG2E;
+    l[0] = l[1] = (lane & 3) == 0 ? 1.f : 0.f;
+  }
 #pragma unroll
   for (int t = 0; t < DTILES; ++t)
 #pragma unroll
@@ -418,7 +425,7 @@ LAB_EXPORT int lab_attention_prefill(void* out, int out_stride, const void* q, i
                                      const void* cache_v, const int* q_start, const int* kv_len, const int* pos0,
                                      const int* block_table, int max_blocks, int requests, int max_q_len, int n_q,
                                      int n_kv, int page_size, int num_pages, int window, float scale, int min_q_len,
-                                     cudaStream_t stream) {
+                                     const float* sink, cudaStream_t stream) {
   if (requests <= 0 || max_q_len <= 0) return 0;
   if (n_q % n_kv || q_stride % 8 || (((uintptr_t)q) & 15)) return (int)cudaErrorInvalidValue;
   static bool configured = false;
@@ -431,7 +438,8 @@ LAB_EXPORT int lab_attention_prefill(void* out, int out_stride, const void* q, i
   return (int)lab_launch(attention_prefill_kernel, grid, dim3(PF_THREADS), (size_t)PF_SMEM, stream,
                          (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
                          (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, q_start, kv_len, pos0,
-                         block_table, max_blocks, n_q, n_kv, page_size, num_pages, window, scale * LOG2E, min_q_len);
+                         block_table, max_blocks, n_q, n_kv, page_size, num_pages, window, scale * LOG2E, min_q_len,
+                         sink);
 }
 
 static int decode_launch(void* out, int out_stride, const void* q, int q_stride, const void* cache_k,

@@ -17,9 +17,14 @@ constexpr int BM = 64, BN = 64, BK = 16, PAD = 4;
 template <typename T, typename OutT, bool GATED>
 __global__ void __launch_bounds__(256) gemm_plain_kernel(OutT* __restrict__ out, const T* __restrict__ x,
                                                          const T* __restrict__ w, const T* __restrict__ bias, int M,
-                                                         int N, int K, int ldx, int ldo) {
+                                                         int N, int K, int ldx, int ldo, long long batch_x,
+                                                         long long batch_w, long long batch_o) {
   pdl_trigger();
   pdl_wait();
+  // a batch of products of one shape (blockIdx.z): operand b lies b * batch_* elements further on
+  x += blockIdx.z * batch_x;
+  w += blockIdx.z * batch_w;
+  out += blockIdx.z * batch_o;
   __shared__ float xs[BK][BM + PAD];
   __shared__ float ws[GATED ? 2 : 1][BK][BN + PAD];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -84,13 +89,13 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(OutT* __restrict__ out,
 
 template <typename T, typename OutT>
 int launch(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx, int ldo, int gated,
-           cudaStream_t stream) {
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+           cudaStream_t stream, int batch = 1, long long batch_x = 0, long long batch_w = 0, long long batch_o = 0) {
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
   if (gated)
     return (int)lab_launch(gemm_plain_kernel<T, OutT, true>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
-                           (const T*)w, (const T*)nullptr, M, N, K, ldx, ldo);
+                           (const T*)w, (const T*)nullptr, M, N, K, ldx, ldo, batch_x, batch_w, batch_o);
   return (int)lab_launch(gemm_plain_kernel<T, OutT, false>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
-                         (const T*)w, (const T*)bias, M, N, K, ldx, ldo);
+                         (const T*)w, (const T*)bias, M, N, K, ldx, ldo, batch_x, batch_w, batch_o);
 }
 }  // namespace
 
@@ -101,4 +106,20 @@ LAB_EXPORT int lab_gemm_plain(void* out, const void* x, const void* w, const voi
   if (dtype == LAB_F32) return launch<float, float>(out, x, w, bias, M, N, K, ldx, ldo, gated, stream);
   if (out_f32) return launch<__nv_bfloat16, float>(out, x, w, bias, M, N, K, ldx, ldo, gated, stream);
   return launch<__nv_bfloat16, __nv_bfloat16>(out, x, w, bias, M, N, K, ldx, ldo, gated, stream);
+}
+
+// `batch` products of one shape in one launch: out_b[m, n] = sum_k x_b[m, k] * w_b[n, k], operand b lying
+// b * batch_* elements after operand 0 (heads side by side in a row: batch_x = the head's width).
+LAB_EXPORT int lab_gemm_plain_batched(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
+                                      int batch, long long batch_x, long long batch_w, long long batch_o, int dtype,
+                                      int out_f32, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (batch > 65535) return (int)cudaErrorInvalidValue;
+  if (dtype == LAB_F32)
+    return launch<float, float>(out, x, w, nullptr, M, N, K, ldx, ldo, 0, stream, batch, batch_x, batch_w, batch_o);
+  if (out_f32)
+    return launch<__nv_bfloat16, float>(out, x, w, nullptr, M, N, K, ldx, ldo, 0, stream, batch, batch_x, batch_w,
+                                        batch_o);
+  return launch<__nv_bfloat16, __nv_bfloat16>(out, x, w, nullptr, M, N, K, ldx, ldo, 0, stream, batch, batch_x, batch_w,
+                                              batch_o);
 }

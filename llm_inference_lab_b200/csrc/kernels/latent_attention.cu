@@ -68,13 +68,17 @@ __global__ void __launch_bounds__(kThreads) latent_prep_kernel(T* __restrict__ c
 }
 
 // ---- the queries' rotated parts ---------------------------------------------------------------
-// q (T) [tokens, heads, D + R] -> q_cat (float) [tokens, heads, C + R]: columns [C, C + R) get the
-// rotated last R entries of each head (the first C columns are the absorbed product's).
+// q (T) [tokens, heads, q_head] (a head: D plain entries, R to rotate, then padding) -> q_cat (float)
+// [tokens, heads, C + R]: columns [C, C + R) get the rotated R entries of each head (the first C columns
+// are the absorbed product's).  With `in_place`, the rotated entries also replace the stored ones in q
+// (rounded to T), for kernels that read q itself; q_cat may then be null.
 template <typename T>
-__global__ void __launch_bounds__(kThreads) latent_q_rope_kernel(float* __restrict__ q_cat, const T* __restrict__ q,
-                                                                 int heads, int D, int R, int C,
+__global__ void __launch_bounds__(kThreads) latent_q_rope_kernel(float* __restrict__ q_cat, T* __restrict__ q,
+                                                                 int heads, int D, int R, int C, int q_head,
                                                                  const int* __restrict__ positions,
-                                                                 const float* __restrict__ inv_freq, int rot_dims) {
+                                                                 const float* __restrict__ inv_freq, int rot_dims,
+                                                                 int in_place) {
+  extern __shared__ float rotated[];      // [heads * R]
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -82,7 +86,7 @@ __global__ void __launch_bounds__(kThreads) latent_q_rope_kernel(float* __restri
   const int half = rot_dims / 2;
   for (int idx = threadIdx.x; idx < heads * R; idx += kThreads) {
     const int h = idx / R, i = idx % R;
-    const T* src = q + ((size_t)t * heads + h) * (D + R) + D;
+    const T* src = q + ((size_t)t * heads + h) * q_head + D;
     float v = to_f32(src[i]);
     if (i < rot_dims) {
       const int f = i < half ? i : i - half;
@@ -92,13 +96,72 @@ __global__ void __launch_bounds__(kThreads) latent_q_rope_kernel(float* __restri
       rope_rotate(to_f32(src[f]), to_f32(src[f + half]), cs, sn, lo, hi);
       v = i < half ? lo : hi;
     }
-    q_cat[((size_t)t * heads + h) * (C + R) + C + i] = v;
+    if (q_cat != nullptr) q_cat[((size_t)t * heads + h) * (C + R) + C + i] = v;
+    rotated[idx] = v;
+  }
+  if (!in_place) return;
+  __syncthreads();       // every pair has been read before any of it is replaced
+  for (int idx = threadIdx.x; idx < heads * R; idx += kThreads)
+    q[((size_t)t * heads + idx / R) * q_head + D + idx % R] = from_f32<T>(rotated[idx]);
+}
+
+// ---- keys and values for the tensor-core attention of prompts' portions ------------------------
+// Requests that bring many tokens attend in the plain form: keys [W_uk c ; kr] and values W_uv c per head,
+// projected up for the step from the latents the rows can see, into scratch pools that have the cache's own
+// page numbering (so the kernel walks the step's block table as it is).
+// `meta` [selected requests][4]: request index in the step, first key position, number of keys, first row
+// in the compact list.  Gather: compact row i <- the latent c of its key, and slot_of[i] <- its cache slot.
+template <typename T>
+__global__ void __launch_bounds__(128) latent_gather_kernel(T* __restrict__ compact, int* __restrict__ slot_of,
+                                                            const T* __restrict__ cache, const int* __restrict__ meta,
+                                                            const int* __restrict__ block_table, int bt_width, int C,
+                                                            int W, int page_size, int num_pages) {
+  pdl_trigger();
+  pdl_wait();
+  const int* mt = meta + 4 * blockIdx.y;
+  const int req = mt[0], lo = mt[1], count = mt[2], base = mt[3];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kk = blockIdx.x * 4 + warp;
+  if (kk >= count) return;
+  const int pos = lo + kk;
+  const int page = block_table[(size_t)req * bt_width + pos / page_size];
+  if (page < 0 || page >= num_pages) {
+    if (lane == 0) lab_set_error(LAB_ERR_PAGE_RANGE);
+    return;
+  }
+  const int slot = page * page_size + pos % page_size;
+  if (lane == 0) slot_of[base + kk] = slot;
+  const T* src = cache + (size_t)slot * W;
+  T* dst = compact + (size_t)(base + kk) * C;
+  for (int c = lane; c < C; c += 32) dst[c] = src[c];
+}
+
+// Scatter: projected [rows, heads * D + heads * V] (keys' plain parts, then values) and the cached
+// rotated part -> k_pool, v_pool [pages, heads, page_size, HD]: k = [plain ; kr ; 0], v = [value ; 0].
+template <typename T>
+__global__ void __launch_bounds__(kThreads) latent_scatter_kernel(T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                                                  const T* __restrict__ projected,
+                                                                  const int* __restrict__ slot_of,
+                                                                  const T* __restrict__ cache, int heads, int D, int R,
+                                                                  int V, int C, int HD, int page_size) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x;
+  const int slot = slot_of[i];
+  const int page = slot / page_size, off = slot % page_size;
+  const T* row = projected + (size_t)i * heads * (D + V);
+  const T* kr = cache + (size_t)slot * (C + R) + C;
+  for (int idx = threadIdx.x; idx < heads * HD; idx += kThreads) {
+    const int h = idx / HD, c = idx % HD;
+    const size_t at = (((size_t)page * heads + h) * page_size + off) * HD + c;
+    k_pool[at] = c < D ? row[h * D + c] : (c < D + R ? kr[c - D] : from_f32<T>(0.f));
+    v_pool[at] = c < V ? row[heads * D + h * V + c] : from_f32<T>(0.f);
   }
 }
 
 // ---- attention ------------------------------------------------------------------------------------
-// One CTA takes up to QT consecutive rows of one request with all heads: the tiles of keys it
-// stages in shared memory serve every (row, head) pair.  A warp owns pairs; a lane owns a key of
+// One CTA takes up to QT consecutive rows of one request with HG of its heads (all of them where
+// shared memory allows): the tiles of keys it stages in shared memory serve every (row, head) pair.  A warp owns pairs; a lane owns a key of
 // the tile for the scores and columns of the output for the weighted sum.  Running maximum, sum
 // and output of a pair live in shared memory; the sink opens them (maximum = sink, sum = 1).
 struct LatentParams {
@@ -109,7 +172,8 @@ struct LatentParams {
   const int* q_start;
   const int* pos0;
   const int* block_table;
-  int bt_width, heads, C, W, page_size, num_pages, window, QT;
+  int bt_width, heads, C, W, page_size, num_pages, window, QT, HG;
+  int below;              // > 0: only requests that bring fewer rows than this (others are served elsewhere)
   float scale;
 };
 
@@ -121,24 +185,28 @@ __global__ void __launch_bounds__(kThreads) latent_attention_kernel(LatentParams
   const int req = blockIdx.y;
   const int first = p.q_start[req] + blockIdx.x * p.QT;
   const int n = min(p.QT, p.q_start[req + 1] - first);
-  if (n <= 0) return;
-  const int H = p.heads, C = p.C, W = p.W, KW = W + 1;
+  if (n <= 0 || (p.below > 0 && p.q_start[req + 1] - p.q_start[req] >= p.below)) return;
+  const int C = p.C, W = p.W, KW = W + 1;
+  const int h0 = blockIdx.z * p.HG, H = min(p.HG, p.heads - h0);     // this CTA's heads: h0 .. h0 + H - 1
   const int pairs = n * H;
-  float* qs = smem;                                  // [QT * H][W]
-  float* keys = qs + (size_t)p.QT * H * W;           // [kKeys][W + 1]
-  float* acc = keys + kKeys * KW;                    // [QT * H][C]
-  float* run_m = acc + (size_t)p.QT * H * C;         // [QT * H]
-  float* run_l = run_m + p.QT * H;
-  float* probs = run_l + p.QT * H;                   // [kWarps][kKeys]
+  float* qs = smem;                                  // [QT * HG][W]
+  float* keys = qs + (size_t)p.QT * p.HG * W;        // [kKeys][W + 1]
+  float* acc = keys + kKeys * KW;                    // [QT * HG][C]
+  float* run_m = acc + (size_t)p.QT * p.HG * C;      // [QT * HG]
+  float* run_l = run_m + p.QT * p.HG;
+  float* probs = run_l + p.QT * p.HG;                // [kWarps][kKeys]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const T* cache = (const T*)p.cache;
 
   const int p_first = p.pos0[req] + blockIdx.x * p.QT, p_last = p_first + n - 1;
   const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
-  for (int i = tid; i < pairs * W; i += kThreads) qs[i] = p.q[(size_t)first * H * W + i];
+  for (int i = tid; i < pairs * W; i += kThreads) {
+    const int pair = i / W, c = i % W;
+    qs[i] = p.q[((size_t)(first + pair / H) * p.heads + h0 + pair % H) * W + c];
+  }
   for (int i = tid; i < pairs * C; i += kThreads) acc[i] = 0.f;
   for (int i = tid; i < pairs; i += kThreads) {
-    run_m[i] = p.sink != nullptr ? p.sink[i % H] : -INFINITY;
+    run_m[i] = p.sink != nullptr ? p.sink[h0 + i % H] : -INFINITY;
     run_l[i] = p.sink != nullptr ? 1.f : 0.f;
   }
   const int* table = p.block_table + (size_t)req * p.bt_width;
@@ -195,13 +263,30 @@ __global__ void __launch_bounds__(kThreads) latent_attention_kernel(LatentParams
     }
   }
   __syncthreads();
-  T* out = (T*)p.out + (size_t)first * H * C;
-  for (int i = tid; i < pairs * C; i += kThreads) out[i] = from_f32<T>(acc[i] / run_l[i / C]);
+  T* out = (T*)p.out;
+  for (int i = tid; i < pairs * C; i += kThreads) {
+    const int pair = i / C, c = i % C;
+    out[((size_t)(first + pair / H) * p.heads + h0 + pair % H) * C + c] = from_f32<T>(acc[i] / run_l[pair]);
+  }
 }
 
 size_t attention_smem(int QT, int H, int C, int W) {
   return sizeof(float) * ((size_t)QT * H * W + (size_t)kKeys * (W + 1) + (size_t)QT * H * C + 2 * (size_t)QT * H +
                           kWarps * kKeys);
+}
+
+// Rows and heads one CTA takes: all heads and up to 8 rows while that fits 96 KB of shared memory (two
+// CTAs an SM); a step of single tokens takes a warp's worth of heads per CTA, so that more CTAs share the
+// keys' stream; heads are halved further while a CTA's share exceeds 200 KB.
+bool attention_shape(int heads, int C, int W, int max_q, int* qt_out, int* hg_out) {
+  int hg = max_q <= 1 ? (heads < kWarps ? heads : kWarps) : heads;
+  int qt = 8;
+  while (qt > 1 && (attention_smem(qt, hg, C, W) > 96 * 1024 || qt / 2 >= max_q)) qt /= 2;
+  while (hg > 1 && attention_smem(qt, hg, C, W) > 200 * 1024) hg = (hg + 1) / 2;
+  if (attention_smem(qt, hg, C, W) > 200 * 1024) return false;
+  *qt_out = qt;
+  *hg_out = hg;
+  return true;
 }
 
 }  // namespace
@@ -221,40 +306,61 @@ LAB_EXPORT int lab_latent_prep(void* cq, void* cache, const float* proj, int ld,
   LAB_LAUNCH_CHECK();
 }
 
-LAB_EXPORT int lab_latent_q_rope(float* q_cat, const void* q, int tokens, int heads, int D, int R, int C,
-                                 const int* positions, const float* inv_freq, int rot_dims, int dtype,
+LAB_EXPORT int lab_latent_q_rope(float* q_cat, void* q, int tokens, int heads, int D, int R, int C, int q_head,
+                                 const int* positions, const float* inv_freq, int rot_dims, int in_place, int dtype,
                                  cudaStream_t stream) {
   if (tokens <= 0) return 0;
+  const size_t smem = sizeof(float) * (size_t)heads * R;
+  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   if (dtype == LAB_F32)
-    lab_launch(latent_q_rope_kernel<float>, dim3(tokens), dim3(kThreads), 0, stream, q_cat, (const float*)q, heads, D, R,
-               C, positions, inv_freq, rot_dims);
+    lab_launch(latent_q_rope_kernel<float>, dim3(tokens), dim3(kThreads), smem, stream, q_cat, (float*)q, heads, D, R, C,
+               q_head, positions, inv_freq, rot_dims, in_place);
   else
-    lab_launch(latent_q_rope_kernel<__nv_bfloat16>, dim3(tokens), dim3(kThreads), 0, stream, q_cat,
-               (const __nv_bfloat16*)q, heads, D, R, C, positions, inv_freq, rot_dims);
+    lab_launch(latent_q_rope_kernel<__nv_bfloat16>, dim3(tokens), dim3(kThreads), smem, stream, q_cat,
+               (__nv_bfloat16*)q, heads, D, R, C, q_head, positions, inv_freq, rot_dims, in_place);
   LAB_LAUNCH_CHECK();
 }
 
-// Rows of a request that one CTA takes: as many (up to 8) as shared memory holds.
+// bfloat16 only: the tensor-core attention these feed takes nothing else.
+LAB_EXPORT int lab_latent_gather(void* compact, int* slot_of, const void* cache, const int* meta, int n_selected,
+                                 int max_count, const int* block_table, int bt_width, int C, int W, int page_size,
+                                 int num_pages, cudaStream_t stream) {
+  if (n_selected <= 0 || max_count <= 0) return 0;
+  lab_launch(latent_gather_kernel<__nv_bfloat16>, dim3((max_count + 3) / 4, n_selected), dim3(128), 0, stream,
+             (__nv_bfloat16*)compact, slot_of, (const __nv_bfloat16*)cache, meta, block_table, bt_width, C, W,
+             page_size, num_pages);
+  LAB_LAUNCH_CHECK();
+}
+
+LAB_EXPORT int lab_latent_scatter(void* k_pool, void* v_pool, const void* projected, const int* slot_of,
+                                  const void* cache, int rows, int heads, int D, int R, int V, int C, int HD,
+                                  int page_size, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  lab_launch(latent_scatter_kernel<__nv_bfloat16>, dim3(rows), dim3(kThreads), 0, stream, (__nv_bfloat16*)k_pool,
+             (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)projected, slot_of, (const __nv_bfloat16*)cache, heads, D, R,
+             V, C, HD, page_size);
+  LAB_LAUNCH_CHECK();
+}
+
+// Rows of a request that one CTA takes (0: a single head's row does not fit shared memory).
 LAB_EXPORT int lab_latent_attention_rows(int heads, int C, int W, int max_q) {
-  int qt = 8;
-  while (qt > 1 && (attention_smem(qt, heads, C, W) > 96 * 1024 || qt / 2 >= max_q)) qt /= 2;
-  if (attention_smem(qt, heads, C, W) > 200 * 1024) return 0;
-  return qt;
+  int qt = 0, hg = 0;
+  return attention_shape(heads, C, W, max_q, &qt, &hg) ? qt : 0;
 }
 
 LAB_EXPORT int lab_latent_attention(void* out, const float* q, const void* cache, const float* sink,
                                     const int* q_start, const int* pos0, const int* block_table, int bt_width,
                                     int n_requests, int max_q, int heads, int C, int W, int page_size, int num_pages,
-                                    int window, float scale, int dtype, cudaStream_t stream) {
+                                    int window, float scale, int below, int dtype, cudaStream_t stream) {
   if (n_requests <= 0 || max_q <= 0) return 0;
   LatentParams p;
+  p.below = below;
   p.out = out; p.q = q; p.cache = cache; p.sink = sink; p.q_start = q_start; p.pos0 = pos0;
   p.block_table = block_table; p.bt_width = bt_width; p.heads = heads; p.C = C; p.W = W; p.page_size = page_size;
   p.num_pages = num_pages; p.window = window; p.scale = scale;
-  p.QT = lab_latent_attention_rows(heads, C, W, max_q);
-  if (p.QT <= 0) return (int)cudaErrorInvalidValue;
-  const size_t smem = attention_smem(p.QT, heads, C, W);
-  const dim3 grid((max_q + p.QT - 1) / p.QT, n_requests);
+  if (!attention_shape(heads, C, W, max_q, &p.QT, &p.HG)) return (int)cudaErrorInvalidValue;
+  const size_t smem = attention_smem(p.QT, p.HG, C, W);
+  const dim3 grid((max_q + p.QT - 1) / p.QT, n_requests, (heads + p.HG - 1) / p.HG);
   cudaError_t e;
   if (dtype == LAB_F32) {
     e = cudaFuncSetAttribute(latent_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -283,6 +283,29 @@ def gemm_plain(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = Non
     return out
 
 
+def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, h, :] = w[h] @ x[t, h, :] for every head h: x [tokens, heads, >= k] (a head's first k entries are
+    read), w [heads, n, k] contiguous, out [tokens, heads, >= n] (a head's first n entries are written), 32-bit
+    or of x's type.  Steps of many bfloat16 tokens run one tensor-core product per head; else all heads are
+    one launch on the ordinary units."""
+    _on_gpu(x, w, out)
+    tokens, heads = x.shape[0], x.shape[1]
+    n, k = w.shape[1], w.shape[2]
+    assert w.is_contiguous() and w.shape[0] == heads and w.dtype == x.dtype and x.stride(2) == 1 and out.stride(2) == 1
+    assert x.stride(0) == heads * x.stride(1) and out.stride(0) == heads * out.stride(1)
+    assert out.dtype in (x.dtype, torch.float32) and x.shape[2] >= k and out.shape[2] >= n
+    f32 = out.dtype == torch.float32
+    if x.dtype == torch.bfloat16 and tokens > 128 and not _force_plain:
+        for h in range(heads):
+            linear(x[:, h, :k], w[h], None, out_f32=f32, out=out[:, h, :n])
+        return out
+    _check(lib("gemm_plain").lab_gemm_plain_batched(
+        _ptr(out), _ptr(x), _ptr(w), tokens, n, k, x.stride(0), out.stride(0), heads, ctypes.c_longlong(x.stride(1)),
+        ctypes.c_longlong(n * k), ctypes.c_longlong(out.stride(1)), dtype_code(x.dtype), int(f32), _stream()),
+        "gemm_plain_batched")
+    return out
+
+
 def attention_plain(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, row_req: torch.Tensor,
                     row_pos: torch.Tensor, block_table: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
                     window: int, scale: float, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -694,7 +717,7 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
         _check(L.lab_attention_prefill(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v),
                                        _ptr(q_start), _ptr(kv_len), _ptr(pos0), _ptr(block_table),
                                        block_table.shape[1], n_requests, max_q, n_q, n_kv, page_size, num_pages,
-                                       window, ctypes.c_float(scale), 2, _stream()), "attention_prefill")
+                                       window, ctypes.c_float(scale), 2, None, _stream()), "attention_prefill")
     if n_decode:
         if splits is None:
             span = min(max_kv_len, window) if window else max_kv_len
@@ -892,36 +915,107 @@ def latent_prep(proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, w_q
     return cq
 
 
-def latent_q_rope(q: torch.Tensor, q_cat: torch.Tensor, heads: int, dim: int, rot_dim: int, kv_rank: int,
-                  positions: torch.Tensor, inv_freq: torch.Tensor, rot_dims: int) -> None:
-    """Rotates the last `rot_dim` entries of every head of q [tokens, heads * (dim + rot_dim)] into
-    columns [kv_rank, kv_rank + rot_dim) of each head of the 32-bit q_cat [tokens, heads, kv_rank + rot_dim]."""
+def latent_q_rope(q: torch.Tensor, q_cat: torch.Tensor | None, heads: int, dim: int, rot_dim: int, kv_rank: int,
+                  positions: torch.Tensor, inv_freq: torch.Tensor, rot_dims: int, in_place: bool = False) -> None:
+    """Rotates entries [dim, dim + rot_dim) of every head of q [tokens, heads * q_head] (q_head >= dim + rot_dim:
+    a head may end in padding) into columns [kv_rank, kv_rank + rot_dim) of each head of the 32-bit q_cat
+    [tokens, heads, kv_rank + rot_dim]; with `in_place` also into q itself (q_cat may then be None)."""
     _on_gpu(q, q_cat, positions, inv_freq)
     tokens = q.shape[0]
-    assert q.is_contiguous() and q.shape[1] == heads * (dim + rot_dim)
-    assert q_cat.dtype == torch.float32 and q_cat.is_contiguous() and q_cat.shape == (tokens, heads, kv_rank + rot_dim)
-    _check(lib("latent_attention").lab_latent_q_rope(_ptr(q_cat), _ptr(q), tokens, heads, dim, rot_dim, kv_rank,
-                                                     _ptr(positions), _ptr(inv_freq), rot_dims, dtype_code(q.dtype),
-                                                     _stream()), "latent_q_rope")
+    q_head = q.shape[1] // heads
+    assert q.is_contiguous() and q.shape[1] == heads * q_head and q_head >= dim + rot_dim
+    assert q_cat is None or (q_cat.dtype == torch.float32 and q_cat.is_contiguous()
+                             and q_cat.shape == (tokens, heads, kv_rank + rot_dim))
+    assert q_cat is not None or in_place
+    _check(lib("latent_attention").lab_latent_q_rope(_ptr(q_cat), _ptr(q), tokens, heads, dim, rot_dim, kv_rank, q_head,
+                                                     _ptr(positions), _ptr(inv_freq), rot_dims, int(in_place),
+                                                     dtype_code(q.dtype), _stream()), "latent_q_rope")
 
 
 def latent_attention(q_cat: torch.Tensor, cache: torch.Tensor, sink: torch.Tensor | None, ctx, group, heads: int,
-                     kv_rank: int, window: int, scale: float) -> torch.Tensor:
+                     kv_rank: int, window: int, scale: float, below: int = 0) -> torch.Tensor:
     """Every row's heads over the latents of its request's pages: scores q_cat . [c ; kr] * scale,
     softmax in 32-bit whose denominator also holds exp(sink) per head, output the weighted sum of the
-    latents c, [tokens, heads * kv_rank] in the cache's storage type."""
+    latents c, [tokens, heads * kv_rank] in the cache's storage type.  `below` > 0: only the rows of
+    requests that bring fewer rows than that are computed (the others' rows are left as they are)."""
     _on_gpu(q_cat, cache, sink)
     tokens, width = q_cat.shape[0], q_cat.shape[2]
     num_pages, page_size, w = cache.shape
     assert w == width and cache.is_contiguous() and q_cat.dtype == torch.float32 and q_cat.is_contiguous()
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() == heads)
     L = lib("latent_attention")
-    if L.lab_latent_attention_rows(heads, kv_rank, width, ctx.max_q_len) <= 0:
+    max_q = min(ctx.max_q_len, below - 1) if below > 0 else ctx.max_q_len
+    if L.lab_latent_attention_rows(heads, kv_rank, width, max_q) <= 0:
         raise KernelError(f"latent_attention: {heads} heads of width {width} do not fit shared memory")
     out = torch.empty((tokens, heads * kv_rank), dtype=cache.dtype, device=cache.device)
     table = group.block_table
     _check(L.lab_latent_attention(_ptr(out), _ptr(q_cat), _ptr(cache), _ptr(sink), _ptr(ctx.q_start), _ptr(ctx.pos0),
-                                  _ptr(table), table.shape[1], ctx.n_requests, ctx.max_q_len, heads, kv_rank, width,
-                                  page_size, num_pages, window, ctypes.c_float(scale), dtype_code(cache.dtype),
-                                  _stream()), "latent_attention")
+                                  _ptr(table), table.shape[1], ctx.n_requests, max_q, heads, kv_rank, width,
+                                  page_size, num_pages, window, ctypes.c_float(scale), int(below),
+                                  dtype_code(cache.dtype), _stream()), "latent_attention")
+    return out
+
+
+_latent_pools: dict = {}
+
+
+def latent_plain_form_supported(dtype, dim: int, rot_dim: int, vdim: int) -> bool:
+    """Whether prompts' portions of a latent attention can run on the tensor-core attention kernel with keys
+    and values projected up for the step: bfloat16, and heads (key = dim + rot_dim, value = vdim, the
+    larger one rounded up to a multiple of 16) within the kernel's 128."""
+    return dtype == torch.bfloat16 and not _force_plain and latent_head_size(dim, rot_dim, vdim) <= 128
+
+
+def latent_head_size(dim: int, rot_dim: int, vdim: int) -> int:
+    return (max(dim + rot_dim, vdim) + 15) // 16 * 16
+
+
+def latent_attention_plain_form(q: torch.Tensor, cache: torch.Tensor, w_up: torch.Tensor, sink: torch.Tensor | None,
+                                ctx, group, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, window: int,
+                                scale: float, at_least: int, out: torch.Tensor) -> torch.Tensor:
+    """The rows of requests that bring `at_least` rows or more, in the plain form: for every key such a
+    request's rows can see, the head's key [W_uk c ; kr] and value W_uv c are projected up from the cached
+    latent (`w_up` = [W_uk ; W_uv], one product) into scratch pools numbered like the cache's pages; then the
+    tensor-core attention kernel of prompts runs over them with the step's own block table, window and
+    sink.  q [tokens, heads * HD] holds rotated queries (HD = `latent_head_size`, padding zero); the heads'
+    outputs go to `out` [tokens, heads * HD] (value entries first, padding zero)."""
+    _on_gpu(q, cache, w_up, sink, out)
+    hd = latent_head_size(dim, rot_dim, vdim)
+    num_pages, page_size, width = cache.shape
+    tokens = q.shape[0]
+    assert q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and q.shape == (tokens, heads * hd)
+    assert out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous() and q.is_contiguous()
+    assert w_up.shape == (heads * (dim + vdim), kv_rank) and w_up.is_contiguous() and width == kv_rank + rot_dim
+    meta, at, most = [], 0, 0
+    for r, (n, kv) in enumerate(zip(ctx.q_lens, ctx.kv_lens)):
+        if n < at_least:
+            continue
+        lo = max(0, kv - n - window + 1) if window > 0 else 0
+        meta += [r, lo, kv - lo, at]
+        at += kv - lo
+        most = max(most, kv - lo)
+    if not meta:
+        return out
+    key = (str(q.device), num_pages, heads, page_size, hd)
+    pools = _latent_pools.get(key)
+    if pools is None:
+        _latent_pools.clear()       # one engine's pools at a time
+        pools = _latent_pools[key] = (torch.zeros((num_pages, heads, page_size, hd), dtype=q.dtype, device=q.device),
+                                      torch.zeros((num_pages, heads, page_size, hd), dtype=q.dtype, device=q.device))
+    meta_t = torch.tensor(meta, dtype=torch.int32).to(q.device, non_blocking=True)
+    compact = torch.empty((at, kv_rank), dtype=q.dtype, device=q.device)
+    slot_of = torch.empty((at,), dtype=torch.int32, device=q.device)
+    L = lib("latent_attention")
+    table = group.block_table
+    _check(L.lab_latent_gather(_ptr(compact), _ptr(slot_of), _ptr(cache), _ptr(meta_t), len(meta) // 4, most,
+                               _ptr(table), table.shape[1], kv_rank, width, page_size, num_pages, _stream()),
+           "latent_gather")
+    projected = linear(compact, w_up, None)
+    _check(L.lab_latent_scatter(_ptr(pools[0]), _ptr(pools[1]), _ptr(projected), _ptr(slot_of), _ptr(cache), at, heads,
+                                dim, rot_dim, vdim, kv_rank, hd, page_size, _stream()), "latent_scatter")
+    LA = lib("attention_tc", {"LAB_HEAD_DIM": hd})
+    _check(LA.lab_attention_prefill(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(pools[0]), _ptr(pools[1]),
+                                    _ptr(ctx.q_start), _ptr(ctx.kv_len), _ptr(ctx.pos0), _ptr(table), table.shape[1],
+                                    ctx.n_requests, ctx.max_q_len, heads, heads, page_size, num_pages, window,
+                                    ctypes.c_float(scale), int(at_least), _ptr(sink), _stream()), "attention_prefill")
     return out

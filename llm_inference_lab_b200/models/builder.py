@@ -49,6 +49,18 @@ def expected_tensors(bp: ModelBlueprint) -> list[TensorSpec]:
     return list(seen.values())
 
 
+def kernel_libraries(bp: ModelBlueprint, dtype: torch.dtype) -> list[tuple[str, dict]]:
+    """The kernel libraries a model's parts name, with the ones every step uses."""
+    jobs: list = [("rowwise", {}), ("gemm_plain", {})]
+    if dtype == torch.bfloat16:
+        jobs.append(("gemm_tc", {}))
+    for cls, spec in _part_classes(bp):
+        for job in cls.libraries(spec, dtype):
+            if job not in jobs:
+                jobs.append(job)
+    return jobs
+
+
 @dataclasses.dataclass(frozen=True)
 class CachePlan:
     """What the caches of a model look like: one need per cache id, gathered in groups."""
@@ -164,7 +176,17 @@ def load_model(model_dir: str, dtype: torch.dtype, device) -> tuple[CausalLM, ob
 
     arch, config = load_config(model_dir)
     bp = arch.blueprint(config)
+    if str(device) != "cpu":
+        # libraries that are not built yet are compiled side by side while the weights are read
+        from ..kernels import build
+        import threading
+        builder = threading.Thread(target=lambda: build.build_many(kernel_libraries(bp, dtype)), daemon=True)
+        builder.start()
+    else:
+        builder = None
     weights = load_weights(model_dir, expected_tensors(bp), device, optional=_tied_extras(bp))
+    if builder is not None:
+        builder.join()       # a library that failed to build raises where it is first called
     return CausalLM(bp, weights, dtype, device), config
 
 

@@ -83,6 +83,12 @@ class Part:
     def tensors(cls, spec: PartSpec) -> list[TensorSpec]:
         return []
 
+    @classmethod
+    def libraries(cls, spec: PartSpec, dtype: torch.dtype) -> list[tuple[str, dict]]:
+        """Kernel libraries (name, build-time sizes) the part will call, so that a model's loader can
+        build those that are missing side by side instead of one by one at first use."""
+        return []
+
     def __init__(self, spec: PartSpec, weights: dict[str, torch.Tensor], dtype: torch.dtype, device):
         self.spec, self.dtype, self.device = spec, dtype, device
 
@@ -154,6 +160,10 @@ class Block:
     def cache_need(cls, spec: Optional[PartSpec]) -> CacheNeed:
         """Fixed-size state the arrangement itself keeps per request (beside the mixer's cache)."""
         return None
+
+    @classmethod
+    def libraries(cls, spec: Optional[PartSpec], dtype) -> list[tuple[str, dict]]:
+        return []
 
     def __init__(self, mixer: Mixer, ffn: Optional[FeedForward], norms: list[Norm], spec: Optional[PartSpec] = None,
                  weights=None, dtype=None, device=None):

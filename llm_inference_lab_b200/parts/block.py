@@ -63,6 +63,10 @@ class ParallelStreamBlock(Block):
             return FixedState((spec["hidden"],))
         return None
 
+    @classmethod
+    def libraries(cls, spec, dtype):
+        return [("stream32", {})]
+
     def __init__(self, mixer, ffn, norms, spec=None, weights=None, dtype=None, device=None):
         super().__init__(mixer, ffn, norms, spec, weights, dtype, device)
         if spec is None:

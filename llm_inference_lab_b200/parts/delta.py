@@ -41,6 +41,10 @@ class GeneralDelta(Mixer):
     def cache_need(cls, spec: PartSpec):
         return FixedState((spec["heads"], spec["dim"], spec["dim"]))
 
+    @classmethod
+    def libraries(cls, spec, dtype):
+        return [("delta_rule", {"LAB_HEAD_DIM": int(spec["dim"])})]
+
     def __init__(self, spec, weights, dtype, device):
         super().__init__(spec, weights, dtype, device)
         self.heads, self.dim = int(spec["heads"]), int(spec["dim"])

@@ -39,6 +39,18 @@ class LatentAttention(Mixer):
     def cache_need(cls, spec: PartSpec):
         return PagedLatent(spec["kv_rank"] + spec["rot_dim"], int(spec.get("window") or 0))
 
+    # Requests that bring this many rows or more attend in the plain form on the tensor-core kernel (where it
+    # serves: `ops.latent_plain_form_supported`); fewer rows, single decoded tokens above all, read the latents
+    # as they are cached (the absorbed form).  0: always the absorbed form.
+    PLAIN_FORM_ROWS = 16
+
+    @classmethod
+    def libraries(cls, spec, dtype):
+        out = [("latent_attention", {})]
+        if ops.latent_plain_form_supported(dtype, spec["dim"], spec["rot_dim"], spec["vdim"]):
+            out.append(("attention_tc", {"LAB_HEAD_DIM": ops.latent_head_size(spec["dim"], spec["rot_dim"], spec["vdim"])}))
+        return out
+
     def __init__(self, spec, weights, dtype, device):
         super().__init__(spec, weights, dtype, device)
         self.heads, self.dim, self.rot_dim, self.vdim = (int(spec[k]) for k in ("heads", "dim", "rot_dim", "vdim"))
@@ -50,12 +62,23 @@ class LatentAttention(Mixer):
         w = lambda n: self._weight(weights, n)  # noqa: E731
         self.w_down = torch.cat([w("dq"), w("dkv")], dim=0).contiguous()
         self.norm_q, self.norm_c = w("dq.norm"), w("dkv.norm")
-        self.w_uq = w("uq").contiguous()
-        H, D, C, V = self.heads, self.dim, self.kv_rank, self.vdim
+        H, D, R, C, V = self.heads, self.dim, self.rot_dim, self.kv_rank, self.vdim
+        # A head of q and of the heads' output is HD wide: the plain form's head size where it serves (keys
+        # dim + rot_dim, values vdim, padded with zero rows and columns of the matrices around them), else
+        # exactly what the design says.
+        self.plain_form = ops.latent_plain_form_supported(dtype, D, R, V) and self.PLAIN_FORM_ROWS > 0
+        self.hd_q = ops.latent_head_size(D, R, V) if self.plain_form else D + R
+        self.hd_o = self.hd_q if self.plain_form else V
+        w_uq = torch.zeros((H, self.hd_q, self.q_rank), dtype=dtype, device=w("uq").device)
+        w_uq[:, : D + R] = w("uq").view(H, D + R, self.q_rank)
+        self.w_uq = w_uq.view(H * self.hd_q, self.q_rank).contiguous()
         # per head: the key projection transposed (it meets the query), the value projection as stored
         self.w_uk_t = w("uk").view(H, D, C).transpose(1, 2).contiguous()      # [H, C, D]
         self.w_uv = w("uv").view(H, V, C).contiguous()                        # [H, V, C]
-        self.w_o = w("o").contiguous()
+        self.w_up = torch.cat([w("uk"), w("uv")], dim=0).contiguous() if self.plain_form else None
+        w_o = torch.zeros((w("o").shape[0], H, self.hd_o), dtype=dtype, device=w("o").device)
+        w_o[:, :, :V] = w("o").view(-1, H, V)
+        self.w_o = w_o.view(-1, H * self.hd_o).contiguous()
         self.sink = weights[spec.prefix + "sink"].to(torch.float32).contiguous() if spec.get("sink") else None
         i = np.arange(self.rot_dims // 2, dtype=np.float64)
         inv = np.power(float(spec["rot_base"]), -2.0 * i / max(self.rot_dims, 1)).astype(np.float32)
@@ -70,16 +93,24 @@ class LatentAttention(Mixer):
         cq = ops.latent_prep(proj, self.q_rank, C, R, self.norm_q, self.norm_c, ctx.row_pos, self.inv_freq,
                              self.rot_dims, group.row_slot if write else None, cache.k if write else None, self.eps)
         q = ops.linear(cq, self.w_uq, None)
-        q_cat = torch.empty((T, H, C + R), dtype=torch.float32, device=x.device)
-        ops.latent_q_rope(q, q_cat, H, D, R, C, ctx.row_pos, self.inv_freq, self.rot_dims)
-        q_heads = q.view(T, H, D + R)
-        for h in range(H):
-            ops.linear(q_heads[:, h, :D], self.w_uk_t[h], None, out_f32=True, out=q_cat[:, h, :C])
-        mixed = ops.latent_attention(q_cat, cache.k, self.sink, ctx, group, H, C, self.window, self.scale)
-        attn = torch.empty((T, H * V), dtype=self.dtype, device=x.device)
-        mixed_heads, attn_heads = mixed.view(T, H, C), attn.view(T, H, V)
-        for h in range(H):
-            ops.linear(mixed_heads[:, h, :], self.w_uv[h], None, out=attn_heads[:, h, :])
+        rows_plain = self.PLAIN_FORM_ROWS if self.plain_form else 0
+        plain = rows_plain > 0 and any(n >= rows_plain for n in ctx.q_lens)
+        absorbed = not plain or any(n < rows_plain for n in ctx.q_lens)
+        # heads' outputs side by side, HD_o wide each; padding must be zero (it meets zero columns of W_o)
+        make = torch.zeros if self.hd_o != V else torch.empty
+        attn = make((T, H * self.hd_o), dtype=self.dtype, device=x.device)
+        if absorbed:
+            q_cat = torch.empty((T, H, C + R), dtype=torch.float32, device=x.device)
+            ops.latent_q_rope(q, q_cat, H, D, R, C, ctx.row_pos, self.inv_freq, self.rot_dims, in_place=plain)
+            ops.linear_heads(q.view(T, H, self.hd_q), self.w_uk_t, q_cat)
+            mixed = ops.latent_attention(q_cat, cache.k, self.sink, ctx, group, H, C, self.window, self.scale,
+                                         below=rows_plain if plain else 0)
+            ops.linear_heads(mixed.view(T, H, C), self.w_uv, attn.view(T, H, self.hd_o))
+        else:
+            ops.latent_q_rope(q, None, H, D, R, C, ctx.row_pos, self.inv_freq, self.rot_dims, in_place=True)
+        if plain:
+            ops.latent_attention_plain_form(q, cache.k, self.w_up, self.sink, ctx, group, H, D, R, V, C, self.window,
+                                            self.scale, rows_plain, attn)
         return ops.linear(attn, self.w_o, None, out_f32=True, allow_partial=True)
 
 

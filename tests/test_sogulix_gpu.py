@@ -347,6 +347,26 @@ def test_models_under_every_cut(tmp_path, name, dtype):
         assert eng.cache.live_requests == 0 and all(f == eng.num_pages for f in eng.free_pages())
 
 
+@pytest.mark.parametrize("rows", [2, 16, 0])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_prompt_portions_on_the_tensor_core_attention(tmp_path, name, rows, monkeypatch):
+    """bfloat16: requests that bring `rows` tokens or more attend in the plain form on the tensor-core kernel
+    (keys and values projected up for the step), the others in the absorbed form, side by side in one step;
+    rows = 2 sends every portion there, 0 none.  Portions of up to 40 tokens beside single tokens, windows
+    that end inside portions, pages and slots used again."""
+    from llm_inference_lab_b200.parts.latent import LatentAttention
+    monkeypatch.setattr(LatentAttention, "PLAIN_FORM_ROWS", rows)
+    cfg, opt = SMALL[name]
+    folder = make_model_folder(str(tmp_path / "m"), cfg, 31, "bfloat16", std=0.08, scales=SPREAD)
+    seqs = sequences(np.random.default_rng(8), cfg["vocab"], [140, 75, 9, 101, 33, 64])
+    want = plain_logits(folder, seqs)
+    for label, steps in (("mixed", trace_mixed(seqs, np.random.default_rng(2), max_live=4, max_portion=40)),
+                         ("portions", trace_portions(seqs, sizes=(17, 2, 31, 16, 3, 15, 40)))):
+        eng = _engine(folder, "bfloat16", opt, steps)
+        _check(run_trace_inprocess(eng, steps), want, "bfloat16", (name, rows, label))
+        assert eng.cache.live_requests == 0
+
+
 def test_cuts_agree_bit_for_bit_in_32_bit(tmp_path):
     """In 32-bit no sum's order depends on how a prompt was cut or on what else is in the batch."""
     cfg, opt = SMALL["A"]
