@@ -10,12 +10,17 @@
 // request's tokens in order, divides each head's o by its root mean square, multiplies by a weight
 // and by sigmoid(gate) and rounds to the storage type for the output projection.
 //
-// One CTA per (head, request).  Built per head size D (LAB_HEAD_DIM).  The columns of S are
-// independent of one another, so thread (j, g) keeps rows g*SL .. g*SL+SL-1 of column j in
-// registers (G = 4 threads per column, sums over rows finished with two shuffles).  Tokens are
-// taken in chunks: the chunk's vectors are prepared in shared memory by all threads, then the
-// threads walk the chunk's tokens without a block-wide barrier.  A step of one token per request
-// (decode) is the same kernel with a chunk of one.
+// One CTA per (head, request, slice of CS columns of S).  Built per head size D (LAB_HEAD_DIM).  The
+// columns of S are independent of one another, so thread (j, g) keeps rows g*SL .. g*SL+SL-1 of column j
+// in registers (G = 4 threads per column, sums over rows finished with two shuffles), and a head's
+// columns are shared out over D / CS CTAs of two warps: what bounds the walk is the number of
+// instructions a token costs each scheduler, so few warps per SM and many SMs serve best.  Tokens are
+// taken in chunks: the chunk's vectors are copied to shared memory by all threads, then the threads
+// walk the chunk's tokens without a block-wide barrier, while the next chunk's values are already on
+// their way from global memory into registers.  Three kernels: a first one, parallel over tokens, forms
+// what does not depend on the state (decays, rates, unit keys); the walk; a third, parallel over tokens,
+// divides each head's raw output by its root mean square and applies weight and gate.  A step of one
+// token per request (decode) is the same three kernels with a chunk of one.
 #include "common.cuh"
 
 #ifndef LAB_HEAD_DIM
@@ -27,41 +32,83 @@ namespace {
 constexpr int D = LAB_HEAD_DIM;
 constexpr int G = 4;
 constexpr int SL = (D + G - 1) / G;
-constexpr int NT = ((D * G + 31) / 32) * 32;
-constexpr int CH = D > 128 ? 4 : 8;
+constexpr int CS = (D % 16 == 0 && D > 16) ? 16 : D;  // columns of S per CTA
+constexpr int NS = D / CS;                           // CTAs per head
+constexpr int NT = ((CS * G + 31) / 32) * 32;
+constexpr int CH = D > 128 ? 4 : (D > 64 ? 8 : 16);  // tokens per chunk
 static_assert(D >= 4 && D <= 256, "head size of the delta rule kernel: 4 to 256");
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 
+// What the walk reads per token and head is one record, prepared by a kernel that is parallel over
+// tokens and copied to shared memory as it is:
+//   u, r * w, w, a * u, k   five vectors over the rows of S, each in the row-block layout below
+//   v                       D values
+//   alpha, beta             alpha = r . (a * u), beta = r . k
+// With them the output needs only the OLD state:
+//   o_j = sum_i r_i S'_ij = (r * w) . S_j  -  alpha (u . S_j)  +  beta v_j
+// so a token costs two independent sums over a column of S (finished by two shuffles) and one update.
+//
+// Row-block layout: thread group g's rows g*SL .. g*SL+SL-1 together, then four floats of padding, so
+// that a thread fetches its share with 16-byte loads, the four groups of a warp hit different banks, and
+// lanes of one group read the same address.  (One 4-byte load per value made shared memory the limit.)
+// Records of one head lie token after token in global memory: a chunk is one contiguous block, brought
+// in by cp.async into the buffer that is not being walked.  (Loads into registers instead, issued before
+// the walk of the chunk before, held the walk's own shared-memory loads back behind them in the load
+// pipe: 2,048 tokens took 1.2 ms either way.)
+constexpr int PV = 5;
+constexpr int SLP = SL + 4;            // a row block with its padding
+constexpr int RL = G * SLP;            // a vector over the rows of S in this layout
+constexpr bool VEC = SL % 4 == 0;
+constexpr int REC = (PV * RL + D + 2 + 3) / 4 * 4;      // floats of a record
+constexpr int OFF_V = PV * RL, OFF_AB = PV * RL + D;
+__device__ __forceinline__ int at_row(int i) { return (i / SL) * SLP + (i % SL); }
+
 struct DeltaParams {
-  void* out;            // [tokens, heads * D] of T
-  const float* r;       // the five projections: [tokens, ld] floats each
-  const float* k;
-  const float* v;
-  const float* g;
-  const float* a;
-  int ld;
-  const float* d;       // decay pre-activation (before its bias) [tokens, ld_d]
-  int ld_d;
-  const void* d_bias;   // [heads * D] of T
-  const void* a_bias;   // [heads * D] of T
-  const void* norm_w;   // [heads * D] of T
+  float* out;           // [tokens, heads * D]: each head's raw output o = S^T r
+  const float* rec;     // [heads][tokens][REC]
+  int tokens;
   float* state;         // [slots, heads, D, D] floats
   const int* q_start;   // [requests + 1]
   const int* state_slot;
   int heads, n_slots, write;
-  float eps, decay_rate;
 };
+
+struct DeltaShared {
+  float rec[2][CH][REC];
+};
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// A thread's SL values of one vector: rows g*SL .. of token `tok`.
+__device__ __forceinline__ void load_rows(float (&dst)[SL], const float* row_block) {
+  if constexpr (VEC) {
+#pragma unroll
+    for (int q = 0; q < SL / 4; ++q) {
+      const float4 t = reinterpret_cast<const float4*>(row_block)[q];
+      dst[4 * q] = t.x, dst[4 * q + 1] = t.y, dst[4 * q + 2] = t.z, dst[4 * q + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int ii = 0; ii < SL; ++ii) dst[ii] = row_block[ii];
+  }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(NT) delta_rule_kernel(DeltaParams p) {
-  __shared__ float s_r[CH][D], s_k[CH][D], s_u[CH][D], s_au[CH][D], s_w[CH][D], s_v[CH][D], s_g[CH][D], s_o[CH][D];
+  extern __shared__ __align__(16) uint8_t delta_smem[];
+  static_assert(!VEC || ((RL * 4) % 16 == 0 && (SLP * 4) % 16 == 0 && REC % 4 == 0), "16-byte loads");
+  DeltaShared& sh = *reinterpret_cast<DeltaShared*>(delta_smem);
   pdl_trigger();
   pdl_wait();
   const int h = blockIdx.x, req = blockIdx.y;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = NT / 32;
-  const int j = tid / G, g = tid % G;
-  const bool live = j < D;
+  const int tid = threadIdx.x;
+  const int j = blockIdx.z * CS + tid / G, g = tid % G;      // this thread's column of S and its rows' block
+  const bool live = tid / G < CS;
   const int row0 = p.q_start[req], row1 = p.q_start[req + 1];
   const int slot = p.state_slot[req];
   if (slot < 0 || slot >= p.n_slots) {
@@ -75,76 +122,61 @@ __global__ void __launch_bounds__(NT) delta_rule_kernel(DeltaParams p) {
     const int i = g * SL + ii;
     S[ii] = (live && i < D) ? S_g[(size_t)i * D + j] : 0.f;
   }
-  const T* d_bias = (const T*)p.d_bias + h * D;
-  const T* a_bias = (const T*)p.a_bias + h * D;
-  const T* norm_w = (const T*)p.norm_w + h * D;
-  T* out = (T*)p.out;
   const int ld_out = p.heads * D;
+  const float* records = p.rec + (size_t)h * p.tokens * REC;
 
-  for (int t0 = row0; t0 < row1; t0 += CH) {
+  // chunk c of the request -> buffer c & 1, sixteen bytes a copy
+  auto fetch = [&](int t0, int buf) {
+    const int n16 = min(CH, row1 - t0) * (REC / 4);
+    const float* src = records + (size_t)t0 * REC;
+    const uint32_t dst = smem_u32(&sh.rec[buf][0][0]);
+    for (int c = tid; c < n16; c += NT) cp_async_16(dst + 16 * c, src + 4 * c);
+    cp_async_commit_group();
+  };
+
+  fetch(row0, 0);
+  int buf = 0;
+  for (int t0 = row0; t0 < row1; t0 += CH, buf ^= 1) {
     const int n = min(CH, row1 - t0);
-    // ---- the chunk's vectors ------------------------------------------------------------
-    for (int idx = tid; idx < n * D; idx += NT) {
-      const int tok = idx / D, i = idx % D;
-      const size_t at = (size_t)(t0 + tok) * p.ld + h * D + i;
-      s_r[tok][i] = p.r[at];
-      s_k[tok][i] = p.k[at];
-      s_v[tok][i] = p.v[at];
-      s_g[tok][i] = sigmoidf_(p.g[at]);
-      s_au[tok][i] = sigmoidf_(p.a[at] + to_f32(a_bias[i]));
-      const float dl = p.d[(size_t)(t0 + tok) * p.ld_d + h * D + i] + to_f32(d_bias[i]);
-      s_w[tok][i] = expf(-p.decay_rate * sigmoidf_(dl));
-    }
-    __syncthreads();
-    for (int tok = warp; tok < n; tok += nwarps) {
-      float ss = 0.f;
-      for (int i = lane; i < D; i += 32) ss += s_k[tok][i] * s_k[tok][i];
-      ss = warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss + 1e-6f);
-      for (int i = lane; i < D; i += 32) {
-        const float u = s_k[tok][i] * inv;
-        s_u[tok][i] = u;
-        s_au[tok][i] *= u;
-      }
-    }
-    __syncthreads();
+    cp_async_wait_all();
+    __syncthreads();       // the chunk has landed for everyone, and the other buffer's readers are done
+    if (t0 + CH < row1) fetch(t0 + CH, buf ^ 1);
     // ---- the recurrence, token by token ---------------------------------------------------
     for (int tok = 0; tok < n; ++tok) {
-      float sa = 0.f;
+      float a0[SL], a1[SL];
+      const float* rec = sh.rec[buf][tok];
+      load_rows(a0, rec + g * SLP);
+      load_rows(a1, rec + RL + g * SLP);
+      float sa0 = 0.f, sa1 = 0.f, rw0 = 0.f, rw1 = 0.f;
 #pragma unroll
-      for (int ii = 0; ii < SL; ++ii) {
-        const int i = g * SL + ii;
-        if (i < D) sa = fmaf(s_u[tok][i], S[ii], sa);
-      }
-      sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-      sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-      const float vj = live ? s_v[tok][j] : 0.f;
-      float o = 0.f;
-#pragma unroll
-      for (int ii = 0; ii < SL; ++ii) {
-        const int i = g * SL + ii;
-        if (i < D) {
-          const float s = fmaf(s_k[tok][i], vj, fmaf(s_w[tok][i], S[ii], -s_au[tok][i] * sa));
-          S[ii] = s;
-          o = fmaf(s, s_r[tok][i], o);
+      for (int ii = 0; ii < SL; ii += 2) {
+        if (g * SL + ii < D) {
+          sa0 = fmaf(a0[ii], S[ii], sa0);
+          rw0 = fmaf(a1[ii], S[ii], rw0);
+        }
+        if (ii + 1 < SL && g * SL + ii + 1 < D) {
+          sa1 = fmaf(a0[ii + 1], S[ii + 1], sa1);
+          rw1 = fmaf(a1[ii + 1], S[ii + 1], rw1);
         }
       }
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      if (live && g == 0) s_o[tok][j] = o;
+      float sa = sa0 + sa1, rw = rw0 + rw1;
+      sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+      rw += __shfl_xor_sync(0xffffffffu, rw, 1);
+      sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+      rw += __shfl_xor_sync(0xffffffffu, rw, 2);
+      const float vj = live ? rec[OFF_V + j] : 0.f;
+      if (live && g == 0)
+        p.out[(size_t)(t0 + tok) * ld_out + h * D + j] = fmaf(rec[OFF_AB + 1], vj, fmaf(-rec[OFF_AB], sa, rw));
+      load_rows(a0, rec + 2 * RL + g * SLP);
+      load_rows(a1, rec + 3 * RL + g * SLP);
+#pragma unroll
+      for (int ii = 0; ii < SL; ++ii)
+        if (g * SL + ii < D) S[ii] = fmaf(a0[ii], S[ii], -a1[ii] * sa);
+      load_rows(a0, rec + 4 * RL + g * SLP);
+#pragma unroll
+      for (int ii = 0; ii < SL; ++ii)
+        if (g * SL + ii < D) S[ii] = fmaf(a0[ii], vj, S[ii]);
     }
-    __syncthreads();
-    // ---- each head's o over its root mean square, weight, gate ------------------------------
-    for (int tok = warp; tok < n; tok += nwarps) {
-      float ss = 0.f;
-      for (int i = lane; i < D; i += 32) ss += s_o[tok][i] * s_o[tok][i];
-      ss = warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss / (float)D + p.eps);
-      for (int i = lane; i < D; i += 32)
-        out[(size_t)(t0 + tok) * ld_out + h * D + i] =
-            from_f32<T>(s_o[tok][i] * inv * to_f32(norm_w[i]) * s_g[tok][i]);
-    }
-    __syncthreads();
   }
   if (p.write) {
 #pragma unroll
@@ -152,6 +184,64 @@ __global__ void __launch_bounds__(NT) delta_rule_kernel(DeltaParams p) {
       const int i = g * SL + ii;
       if (live && i < D) S_g[(size_t)i * D + j] = S[ii];
     }
+  }
+}
+
+// Per token and head, everything of the recurrence that does not depend on the state, in 32-bit:
+// decay w = exp(-rate * sigmoid(d + bias)), removal a = sigmoid(. + bias), unit key u, and the products
+// the walk uses.  One CTA per token, a warp per head at a time.
+template <typename T>
+__global__ void __launch_bounds__(256) delta_prepare_kernel(float* __restrict__ records, int tokens,
+                                                            const float* __restrict__ r, const float* __restrict__ k,
+                                                            const float* __restrict__ v, const float* __restrict__ a,
+                                                            int ld, const float* __restrict__ d, int ld_d,
+                                                            const T* __restrict__ d_bias, const T* __restrict__ a_bias,
+                                                            int heads, float decay_rate) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int h = warp; h < heads; h += 8) {
+    const size_t at = (size_t)t * ld + h * D;
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) ss += k[at + i] * k[at + i];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss + 1e-6f);
+    float* dst = records + ((size_t)h * tokens + t) * REC;
+    float al = 0.f, be = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      const float kk = k[at + i], rr = r[at + i];
+      const float w = expf(-decay_rate * sigmoidf_(d[(size_t)t * ld_d + h * D + i] + to_f32(d_bias[h * D + i])));
+      const float u = kk * inv, au = sigmoidf_(a[at + i] + to_f32(a_bias[h * D + i])) * u;
+      const int ir = at_row(i);
+      dst[ir] = u, dst[RL + ir] = rr * w, dst[2 * RL + ir] = w, dst[3 * RL + ir] = au, dst[4 * RL + ir] = kk;
+      dst[OFF_V + i] = v[at + i];
+      al = fmaf(rr, au, al);
+      be = fmaf(rr, kk, be);
+    }
+    al = warp_sum(al);
+    be = warp_sum(be);
+    if (lane == 0) dst[OFF_AB] = al, dst[OFF_AB + 1] = be;
+  }
+}
+
+// Each head's raw output divided by its root mean square, times a plain weight and sigmoid(gate),
+// rounded to T: one CTA per token, a warp per head at a time.
+template <typename T>
+__global__ void __launch_bounds__(256) delta_finish_kernel(T* __restrict__ out, const float* __restrict__ raw,
+                                                           const float* __restrict__ gate, int ld_gate,
+                                                           const T* __restrict__ norm_w, int heads, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int h = warp; h < heads; h += 8) {
+    const float* o = raw + ((size_t)t * heads + h) * D;
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) ss += o[i] * o[i];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+    for (int i = lane; i < D; i += 32)
+      out[((size_t)t * heads + h) * D + i] =
+          from_f32<T>(o[i] * inv * to_f32(norm_w[h * D + i]) * sigmoidf_(gate[(size_t)t * ld_gate + h * D + i]));
   }
 }
 
@@ -170,21 +260,43 @@ __global__ void __launch_bounds__(256) tanh_cast_kernel(T* __restrict__ out, con
 
 LAB_EXPORT int lab_delta_rule_head_dim() { return D; }
 
-LAB_EXPORT int lab_delta_rule(void* out, const float* r, const float* k, const float* v, const float* g,
-                              const float* a, int ld, const float* d, int ld_d, const void* d_bias,
+// scratch: floats for the heads' raw outputs and the records
+LAB_EXPORT long long lab_delta_rule_scratch(int tokens, int heads) {
+  return (long long)tokens * heads * (D + REC) + REC;
+}
+
+LAB_EXPORT int lab_delta_rule(void* out, float* scratch, const float* r, const float* k, const float* v,
+                              const float* g, const float* a, int ld, const float* d, int ld_d, const void* d_bias,
                               const void* a_bias, const void* norm_w, float* state, const int* q_start,
-                              const int* state_slot, int n_requests, int heads, int n_slots, int write, float eps,
-                              float decay_rate, int dtype, cudaStream_t stream) {
-  if (n_requests <= 0 || heads <= 0) return 0;
+                              const int* state_slot, int tokens, int n_requests, int heads, int n_slots, int write,
+                              float eps, float decay_rate, int dtype, cudaStream_t stream) {
+  if (n_requests <= 0 || heads <= 0 || tokens <= 0) return 0;
+  float* raw = scratch;
+  float* records = raw + (size_t)tokens * heads * D;      // tokens * heads * D is a multiple of 4 floats or not:
+  records += (4 - ((size_t)tokens * heads * D) % 4) % 4;  // records start on 16 bytes (one spare record is asked for)
   DeltaParams p;
-  p.out = out; p.r = r; p.k = k; p.v = v; p.g = g; p.a = a; p.ld = ld; p.d = d; p.ld_d = ld_d;
-  p.d_bias = d_bias; p.a_bias = a_bias; p.norm_w = norm_w; p.state = state; p.q_start = q_start;
-  p.state_slot = state_slot; p.heads = heads; p.n_slots = n_slots; p.write = write; p.eps = eps;
-  p.decay_rate = decay_rate;
-  if (dtype == LAB_F32)
-    lab_launch(delta_rule_kernel<float>, dim3(heads, n_requests), dim3(NT), 0, stream, p);
-  else
-    lab_launch(delta_rule_kernel<__nv_bfloat16>, dim3(heads, n_requests), dim3(NT), 0, stream, p);
+  p.out = raw; p.rec = records; p.tokens = tokens; p.state = state; p.q_start = q_start;
+  p.state_slot = state_slot; p.heads = heads; p.n_slots = n_slots; p.write = write;
+  const size_t smem = sizeof(DeltaShared);
+  const dim3 grid(heads, n_requests, NS);
+  cudaError_t e;
+  if (dtype == LAB_F32) {
+    e = cudaFuncSetAttribute(delta_rule_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    lab_launch(delta_prepare_kernel<float>, dim3(tokens), dim3(256), 0, stream, records, tokens, r, k, v, a, ld, d,
+               ld_d, (const float*)d_bias, (const float*)a_bias, heads, decay_rate);
+    lab_launch(delta_rule_kernel<float>, grid, dim3(NT), smem, stream, p);
+    lab_launch(delta_finish_kernel<float>, dim3(tokens), dim3(256), 0, stream, (float*)out, (const float*)raw, g, ld,
+               (const float*)norm_w, heads, eps);
+  } else {
+    e = cudaFuncSetAttribute(delta_rule_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    lab_launch(delta_prepare_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, records, tokens, r, k, v, a,
+               ld, d, ld_d, (const __nv_bfloat16*)d_bias, (const __nv_bfloat16*)a_bias, heads, decay_rate);
+    lab_launch(delta_rule_kernel<__nv_bfloat16>, grid, dim3(NT), smem, stream, p);
+    lab_launch(delta_finish_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (__nv_bfloat16*)out,
+               (const float*)raw, g, ld, (const __nv_bfloat16*)norm_w, heads, eps);
+  }
   LAB_LAUNCH_CHECK();
 }
 

@@ -159,6 +159,11 @@ __global__ void __launch_bounds__(kThreads) latent_scatter_kernel(T* __restrict_
   }
 }
 
+__device__ __forceinline__ float2 load_pair(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load_pair(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
 // ---- attention ------------------------------------------------------------------------------------
 // One CTA takes up to QT consecutive rows of one request with HG of its heads (all of them where
 // shared memory allows): the tiles of keys it stages in shared memory serve every (row, head) pair.  A warp owns pairs; a lane owns a key of
@@ -174,6 +179,8 @@ struct LatentParams {
   const int* block_table;
   int bt_width, heads, C, W, page_size, num_pages, window, QT, HG;
   int below;              // > 0: only requests that bring fewer rows than this (others are served elsewhere)
+  int splits;             // > 1 (steps of single tokens only): blockIdx.x takes a share of the keys' tiles and
+  float* part;            // leaves (maximum, sum, unnormalised output) here for the merge kernel
   float scale;
 };
 
@@ -183,7 +190,8 @@ __global__ void __launch_bounds__(kThreads) latent_attention_kernel(LatentParams
   pdl_trigger();
   pdl_wait();
   const int req = blockIdx.y;
-  const int first = p.q_start[req] + blockIdx.x * p.QT;
+  const int split = p.splits > 1 ? blockIdx.x : 0, row_block = p.splits > 1 ? 0 : blockIdx.x;
+  const int first = p.q_start[req] + row_block * p.QT;
   const int n = min(p.QT, p.q_start[req + 1] - first);
   if (n <= 0 || (p.below > 0 && p.q_start[req + 1] - p.q_start[req] >= p.below)) return;
   const int C = p.C, W = p.W, KW = W + 1;
@@ -198,33 +206,60 @@ __global__ void __launch_bounds__(kThreads) latent_attention_kernel(LatentParams
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const T* cache = (const T*)p.cache;
 
-  const int p_first = p.pos0[req] + blockIdx.x * p.QT, p_last = p_first + n - 1;
+  const int p_first = p.pos0[req] + row_block * p.QT, p_last = p_first + n - 1;
   const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
   for (int i = tid; i < pairs * W; i += kThreads) {
     const int pair = i / W, c = i % W;
     qs[i] = p.q[((size_t)(first + pair / H) * p.heads + h0 + pair % H) * W + c];
   }
   for (int i = tid; i < pairs * C; i += kThreads) acc[i] = 0.f;
+  const bool with_sink = p.sink != nullptr && split == 0;      // the sink joins one share of the keys only
   for (int i = tid; i < pairs; i += kThreads) {
-    run_m[i] = p.sink != nullptr ? p.sink[h0 + i % H] : -INFINITY;
-    run_l[i] = p.sink != nullptr ? 1.f : 0.f;
+    run_m[i] = with_sink ? p.sink[h0 + i % H] : -INFINITY;
+    run_l[i] = with_sink ? 1.f : 0.f;
   }
   const int* table = p.block_table + (size_t)req * p.bt_width;
 
-  for (int tile = lo / kKeys; tile <= p_last / kKeys; ++tile) {
+  int tile_lo = lo / kKeys, tile_hi = p_last / kKeys;
+  if (p.splits > 1) {
+    const int per = (tile_hi - tile_lo + p.splits) / p.splits;
+    tile_lo += split * per;
+    tile_hi = min(tile_hi, tile_lo + per - 1);
+  }
+  constexpr int kPerWarp = kKeys / kWarps;      // keys of a tile each warp brings in
+  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
     __syncthreads();       // the previous tile's readers are done (and the set-up above is visible)
-    for (int jk = warp; jk < kKeys; jk += kWarps) {
-      const int pos = tile * kKeys + jk;
-      const T* src = nullptr;
+    const T* src[kPerWarp];
+#pragma unroll
+    for (int e = 0; e < kPerWarp; ++e) {
+      const int pos = tile * kKeys + warp * kPerWarp + e;
+      src[e] = nullptr;
       if (pos >= lo && pos <= p_last) {
         const int page = table[pos / p.page_size];
         if (page < 0 || page >= p.num_pages) {
           if (lane == 0) lab_set_error(LAB_ERR_PAGE_RANGE);
         } else {
-          src = cache + ((size_t)page * p.page_size + pos % p.page_size) * W;
+          src[e] = cache + ((size_t)page * p.page_size + pos % p.page_size) * W;
         }
       }
-      for (int c = lane; c < W; c += 32) keys[jk * KW + c] = src != nullptr ? to_f32(src[c]) : 0.f;
+    }
+    if ((W & 1) == 0) {
+      // two entries a load, the loads of a warp's keys in flight together
+      for (int c = 2 * lane; c < W; c += 64) {
+        float2 v[kPerWarp];
+#pragma unroll
+        for (int e = 0; e < kPerWarp; ++e) v[e] = src[e] != nullptr ? load_pair(src[e] + c) : make_float2(0.f, 0.f);
+#pragma unroll
+        for (int e = 0; e < kPerWarp; ++e) {
+          keys[(warp * kPerWarp + e) * KW + c] = v[e].x;
+          keys[(warp * kPerWarp + e) * KW + c + 1] = v[e].y;
+        }
+      }
+    } else {
+      for (int c = lane; c < W; c += 32)
+#pragma unroll
+        for (int e = 0; e < kPerWarp; ++e)
+          keys[(warp * kPerWarp + e) * KW + c] = src[e] != nullptr ? to_f32(src[e][c]) : 0.f;
     }
     __syncthreads();
     for (int pair = warp; pair < pairs; pair += kWarps) {
@@ -263,10 +298,47 @@ __global__ void __launch_bounds__(kThreads) latent_attention_kernel(LatentParams
     }
   }
   __syncthreads();
+  if (p.splits > 1) {
+    // one row per request here: pair = head.  [request][head][split][maximum, sum, output[C]]
+    for (int i = tid; i < pairs * (C + 2); i += kThreads) {
+      const int pair = i / (C + 2), c = i % (C + 2);
+      float* dst = p.part + (((size_t)req * p.heads + h0 + pair) * p.splits + split) * (C + 2);
+      dst[c] = c == 0 ? run_m[pair] : (c == 1 ? run_l[pair] : acc[(size_t)pair * C + c - 2]);
+    }
+    return;
+  }
   T* out = (T*)p.out;
   for (int i = tid; i < pairs * C; i += kThreads) {
     const int pair = i / C, c = i % C;
     out[((size_t)(first + pair / H) * p.heads + h0 + pair % H) * C + c] = from_f32<T>(acc[i] / run_l[pair]);
+  }
+}
+
+// The shares of a single-token request's keys, merged in ascending order of the shares.
+template <typename T>
+__global__ void __launch_bounds__(128) latent_merge_kernel(T* __restrict__ out, const float* __restrict__ part,
+                                                           const int* __restrict__ q_start, int heads, int C,
+                                                           int splits, int below) {
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.x, req = blockIdx.y;
+  const int rows = q_start[req + 1] - q_start[req];
+  if (rows <= 0 || (below > 0 && rows >= below)) return;
+  const float* mine = part + ((size_t)req * heads + h) * splits * (C + 2);
+  float big = -INFINITY;
+  for (int s = 0; s < splits; ++s) big = fmaxf(big, mine[(size_t)s * (C + 2)]);
+  float total = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float m = mine[(size_t)s * (C + 2)];
+    total += m == -INFINITY ? 0.f : expf(m - big) * mine[(size_t)s * (C + 2) + 1];
+  }
+  for (int c = threadIdx.x; c < C; c += 128) {
+    float a = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float m = mine[(size_t)s * (C + 2)];
+      if (m != -INFINITY) a = fmaf(expf(m - big), mine[(size_t)s * (C + 2) + 2 + c], a);
+    }
+    out[((size_t)q_start[req] * heads + h) * C + c] = from_f32<T>(a / total);
   }
 }
 
@@ -351,16 +423,20 @@ LAB_EXPORT int lab_latent_attention_rows(int heads, int C, int W, int max_q) {
 LAB_EXPORT int lab_latent_attention(void* out, const float* q, const void* cache, const float* sink,
                                     const int* q_start, const int* pos0, const int* block_table, int bt_width,
                                     int n_requests, int max_q, int heads, int C, int W, int page_size, int num_pages,
-                                    int window, float scale, int below, int dtype, cudaStream_t stream) {
+                                    int window, float scale, int below, int splits, float* part, int dtype,
+                                    cudaStream_t stream) {
   if (n_requests <= 0 || max_q <= 0) return 0;
+  if (splits > 1 && (max_q != 1 || part == nullptr)) return (int)cudaErrorInvalidValue;
   LatentParams p;
   p.below = below;
+  p.splits = splits < 1 ? 1 : splits;
+  p.part = part;
   p.out = out; p.q = q; p.cache = cache; p.sink = sink; p.q_start = q_start; p.pos0 = pos0;
   p.block_table = block_table; p.bt_width = bt_width; p.heads = heads; p.C = C; p.W = W; p.page_size = page_size;
   p.num_pages = num_pages; p.window = window; p.scale = scale;
   if (!attention_shape(heads, C, W, max_q, &p.QT, &p.HG)) return (int)cudaErrorInvalidValue;
   const size_t smem = attention_smem(p.QT, p.HG, C, W);
-  const dim3 grid((max_q + p.QT - 1) / p.QT, n_requests, (heads + p.HG - 1) / p.HG);
+  const dim3 grid(p.splits > 1 ? p.splits : (max_q + p.QT - 1) / p.QT, n_requests, (heads + p.HG - 1) / p.HG);
   cudaError_t e;
   if (dtype == LAB_F32) {
     e = cudaFuncSetAttribute(latent_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -372,5 +448,19 @@ LAB_EXPORT int lab_latent_attention(void* out, const float* q, const void* cache
     if (e != cudaSuccess) return (int)e;
     lab_launch(latent_attention_kernel<__nv_bfloat16>, grid, dim3(kThreads), smem, stream, p);
   }
+  if (p.splits > 1) {
+    if (dtype == LAB_F32)
+      lab_launch(latent_merge_kernel<float>, dim3(heads, n_requests), dim3(128), 0, stream, (float*)out, part, q_start,
+                 heads, C, p.splits, below);
+    else
+      lab_launch(latent_merge_kernel<__nv_bfloat16>, dim3(heads, n_requests), dim3(128), 0, stream,
+                 (__nv_bfloat16*)out, part, q_start, heads, C, p.splits, below);
+  }
   LAB_LAUNCH_CHECK();
+}
+
+// Heads one CTA of a single-token step takes (the host sizes the shares of the keys by it).
+LAB_EXPORT int lab_latent_attention_heads(int heads, int C, int W, int max_q) {
+  int qt = 0, hg = 0;
+  return attention_shape(heads, C, W, max_q, &qt, &hg) ? hg : 0;
 }

@@ -876,15 +876,18 @@ def delta_rule(proj: torch.Tensor, decay_pre: torch.Tensor, decay_bias: torch.Te
         raise KernelError(f"delta_rule: head size {head_dim} outside 4..256")
     out = torch.empty((tokens, hd), dtype=dt, device=proj.device)
     L = lib("delta_rule", {"LAB_HEAD_DIM": head_dim})
+    L.lab_delta_rule_scratch.restype = ctypes.c_longlong
+    raw = torch.empty((int(L.lab_delta_rule_scratch(tokens, heads)),), dtype=torch.float32, device=proj.device)
     base, esz = proj.data_ptr(), 4
 
     def col(i):
         return ctypes.c_void_p(base + esz * i * hd)
 
-    _check(L.lab_delta_rule(_ptr(out), col(0), col(1), col(2), col(3), col(4), proj.stride(0), _ptr(decay_pre),
-                            decay_pre.stride(0), _ptr(decay_bias), _ptr(rate_bias), _ptr(norm_weight), _ptr(state),
-                            _ptr(ctx.q_start), _ptr(ctx.state_slot), ctx.n_requests, heads, state.shape[0], int(write),
-                            ctypes.c_float(eps), ctypes.c_float(decay_rate), dtype_code(dt), _stream()), "delta_rule")
+    _check(L.lab_delta_rule(_ptr(out), _ptr(raw), col(0), col(1), col(2), col(3), col(4), proj.stride(0),
+                            _ptr(decay_pre), decay_pre.stride(0), _ptr(decay_bias), _ptr(rate_bias), _ptr(norm_weight),
+                            _ptr(state), _ptr(ctx.q_start), _ptr(ctx.state_slot), tokens, ctx.n_requests, heads,
+                            state.shape[0], int(write), ctypes.c_float(eps), ctypes.c_float(decay_rate),
+                            dtype_code(dt), _stream()), "delta_rule", 3)
     return out
 
 
@@ -949,10 +952,20 @@ def latent_attention(q_cat: torch.Tensor, cache: torch.Tensor, sink: torch.Tenso
         raise KernelError(f"latent_attention: {heads} heads of width {width} do not fit shared memory")
     out = torch.empty((tokens, heads * kv_rank), dtype=cache.dtype, device=cache.device)
     table = group.block_table
+    splits, part = 1, None
+    if max_q == 1:
+        # single tokens: the keys' tiles (32 keys each) of a request are shared out over CTAs while the launch
+        # stays within two rounds of the SMs, four tiles a share at least; a merge kernel sums the shares
+        span = min(ctx.max_kv_len, window) if window > 0 else ctx.max_kv_len
+        ctas = ctx.n_requests * -(-heads // max(1, L.lab_latent_attention_heads(heads, kv_rank, width, 1)))
+        splits = int(max(1, min(-(-span // 128), (2 * sm_count()) // max(ctas, 1), 64)))
+        if splits > 1:
+            part = torch.empty((ctx.n_requests * heads * splits * (kv_rank + 2),), dtype=torch.float32,
+                               device=cache.device)
     _check(L.lab_latent_attention(_ptr(out), _ptr(q_cat), _ptr(cache), _ptr(sink), _ptr(ctx.q_start), _ptr(ctx.pos0),
                                   _ptr(table), table.shape[1], ctx.n_requests, max_q, heads, kv_rank, width,
-                                  page_size, num_pages, window, ctypes.c_float(scale), int(below),
-                                  dtype_code(cache.dtype), _stream()), "latent_attention")
+                                  page_size, num_pages, window, ctypes.c_float(scale), int(below), splits, _ptr(part),
+                                  dtype_code(cache.dtype), _stream()), "latent_attention", 2 if splits > 1 else 1)
     return out
 
 
