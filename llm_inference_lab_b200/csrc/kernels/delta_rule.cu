@@ -11,16 +11,19 @@
 // and by sigmoid(gate) and rounds to the storage type for the output projection.
 //
 // One CTA per (head, request, slice of CS columns of S).  Built per head size D (LAB_HEAD_DIM).  The
-// columns of S are independent of one another, so thread (j, g) keeps rows g*SL .. g*SL+SL-1 of column j
-// in registers (G = 4 threads per column, sums over rows finished with two shuffles), and a head's
-// columns are shared out over D / CS CTAs of two warps: what bounds the walk is the number of
-// instructions a token costs each scheduler, so few warps per SM and many SMs serve best.  Tokens are
-// taken in chunks: the chunk's vectors are copied to shared memory by all threads, then the threads
-// walk the chunk's tokens without a block-wide barrier, while the next chunk's values are already on
-// their way from global memory into registers.  Three kernels: a first one, parallel over tokens, forms
-// what does not depend on the state (decays, rates, unit keys); the walk; a third, parallel over tokens,
-// divides each head's raw output by its root mean square and applies weight and gate.  A step of one
-// token per request (decode) is the same three kernels with a chunk of one.
+// columns of S are independent of one another, and so are its rows within a token, so a column is shared
+// out over G threads (4 where D allows): thread g keeps the rows {(q * G + g) * 4 + e} of column j in
+// registers, reads its share of each vector with 16-byte loads (the G threads of a column read a vector's
+// consecutive blocks: no bank conflicts, and lanes of other columns read the same addresses), and the
+// sums over a column are finished by log2(G) shuffles.  What bounds the walk is the chain of dependent
+// instructions one warp has per token (measured with the kernel's own clock: 540 cycles a token with
+// 4 threads a column and 16 rows each), and a head's columns are shared out over D / CS CTAs so that
+// no scheduler holds more than one such chain.  Tokens are taken in chunks:
+// a chunk's records are brought to shared memory by cp.async into the buffer that is not being walked.
+// Three kernels: a first one, parallel over tokens, forms what does not depend on the state (decays,
+// rates, unit keys); the walk; a third, parallel over tokens, divides each head's raw output by its root
+// mean square and applies weight and gate.  A step of one token per request (decode) is the same three
+// kernels with a chunk of one.
 #include "common.cuh"
 
 #ifndef LAB_HEAD_DIM
@@ -30,39 +33,36 @@
 namespace {
 
 constexpr int D = LAB_HEAD_DIM;
-constexpr int G = 4;
-constexpr int SL = (D + G - 1) / G;
+// threads per column: up to 4, so that every thread has whole blocks of four rows.  (Measured at D = 64,
+// 2,048 tokens of one request: 4 threads a column 0.74 ms, 16 threads a column 1.17 ms: a level of
+// shuffles costs the walk about as much as 25 rows a thread.)
+constexpr int G = D % 16 == 0 ? 4 : D % 8 == 0 ? 2 : 1;
+constexpr bool VEC = D % (4 * G) == 0;               // false: one thread a column, one value a load
+constexpr int SL = D / G;                            // rows of a column per thread
 constexpr int CS = (D % 16 == 0 && D > 16) ? 16 : D;  // columns of S per CTA
 constexpr int NS = D / CS;                           // CTAs per head
 constexpr int NT = ((CS * G + 31) / 32) * 32;
-constexpr int CH = D > 128 ? 4 : (D > 64 ? 8 : 16);  // tokens per chunk
+constexpr int CH = 16;                               // tokens per chunk
 static_assert(D >= 4 && D <= 256, "head size of the delta rule kernel: 4 to 256");
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 
 // What the walk reads per token and head is one record, prepared by a kernel that is parallel over
 // tokens and copied to shared memory as it is:
-//   u, r * w, w, a * u, k   five vectors over the rows of S, each in the row-block layout below
+//   u, r * w, w, a * u, k   five vectors over the rows of S
 //   v                       D values
 //   alpha, beta             alpha = r . (a * u), beta = r . k
 // With them the output needs only the OLD state:
 //   o_j = sum_i r_i S'_ij = (r * w) . S_j  -  alpha (u . S_j)  +  beta v_j
-// so a token costs two independent sums over a column of S (finished by two shuffles) and one update.
-//
-// Row-block layout: thread group g's rows g*SL .. g*SL+SL-1 together, then four floats of padding, so
-// that a thread fetches its share with 16-byte loads, the four groups of a warp hit different banks, and
-// lanes of one group read the same address.  (One 4-byte load per value made shared memory the limit.)
-// Records of one head lie token after token in global memory: a chunk is one contiguous block, brought
-// in by cp.async into the buffer that is not being walked.  (Loads into registers instead, issued before
-// the walk of the chunk before, held the walk's own shared-memory loads back behind them in the load
-// pipe: 2,048 tokens took 1.2 ms either way.)
+// so a token costs two independent sums over a column of S and one update, of which only one multiply-add
+// waits for the sums.  Records of one head lie token after token in global memory: a chunk is one
+// contiguous block.  (Loads into registers instead, issued before the walk of the chunk before, held the
+// walk's own shared-memory loads back behind them in the load pipe.)
 constexpr int PV = 5;
-constexpr int SLP = SL + 4;            // a row block with its padding
-constexpr int RL = G * SLP;            // a vector over the rows of S in this layout
-constexpr bool VEC = SL % 4 == 0;
-constexpr int REC = (PV * RL + D + 2 + 3) / 4 * 4;      // floats of a record
-constexpr int OFF_V = PV * RL, OFF_AB = PV * RL + D;
-__device__ __forceinline__ int at_row(int i) { return (i / SL) * SLP + (i % SL); }
+constexpr int REC = (PV * D + D + 2 + 3) / 4 * 4;      // floats of a record
+constexpr int OFF_V = PV * D, OFF_AB = PV * D + D;
+// row of S that thread g holds in register ii
+__device__ __forceinline__ int row_of(int g, int ii) { return VEC ? ((ii / 4) * G + g) * 4 + (ii % 4) : ii; }
 
 struct DeltaParams {
   float* out;           // [tokens, heads * D]: each head's raw output o = S^T r
@@ -84,24 +84,24 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-// A thread's SL values of one vector: rows g*SL .. of token `tok`.
-__device__ __forceinline__ void load_rows(float (&dst)[SL], const float* row_block) {
+// A thread's SL values of one vector of D values in shared memory.
+__device__ __forceinline__ void load_rows(float (&dst)[SL], const float* vec, int g) {
   if constexpr (VEC) {
 #pragma unroll
     for (int q = 0; q < SL / 4; ++q) {
-      const float4 t = reinterpret_cast<const float4*>(row_block)[q];
+      const float4 t = reinterpret_cast<const float4*>(vec)[q * G + g];
       dst[4 * q] = t.x, dst[4 * q + 1] = t.y, dst[4 * q + 2] = t.z, dst[4 * q + 3] = t.w;
     }
   } else {
 #pragma unroll
-    for (int ii = 0; ii < SL; ++ii) dst[ii] = row_block[ii];
+    for (int ii = 0; ii < SL; ++ii) dst[ii] = vec[ii];
   }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(NT) delta_rule_kernel(DeltaParams p) {
   extern __shared__ __align__(16) uint8_t delta_smem[];
-  static_assert(!VEC || ((RL * 4) % 16 == 0 && (SLP * 4) % 16 == 0 && REC % 4 == 0), "16-byte loads");
+  static_assert(REC % 4 == 0 && (!VEC || D % 4 == 0), "16-byte loads");
   DeltaShared& sh = *reinterpret_cast<DeltaShared*>(delta_smem);
   pdl_trigger();
   pdl_wait();
@@ -118,10 +118,7 @@ __global__ void __launch_bounds__(NT) delta_rule_kernel(DeltaParams p) {
   float* S_g = p.state + ((size_t)slot * p.heads + h) * D * D;
   float S[SL];
 #pragma unroll
-  for (int ii = 0; ii < SL; ++ii) {
-    const int i = g * SL + ii;
-    S[ii] = (live && i < D) ? S_g[(size_t)i * D + j] : 0.f;
-  }
+  for (int ii = 0; ii < SL; ++ii) S[ii] = live ? S_g[(size_t)row_of(g, ii) * D + j] : 0.f;
   const int ld_out = p.heads * D;
   const float* records = p.rec + (size_t)h * p.tokens * REC;
 
@@ -143,47 +140,43 @@ __global__ void __launch_bounds__(NT) delta_rule_kernel(DeltaParams p) {
     if (t0 + CH < row1) fetch(t0 + CH, buf ^ 1);
     // ---- the recurrence, token by token ---------------------------------------------------
     for (int tok = 0; tok < n; ++tok) {
-      float a0[SL], a1[SL];
+      // All of the token's values are asked for at once; what does not wait for the sums over the column
+      // (w * S + k * v_j) is formed beside them, so that one multiply-add follows the shuffles.
+      float u[SL], rw_[SL], w[SL], au[SL], kk[SL];
       const float* rec = sh.rec[buf][tok];
-      load_rows(a0, rec + g * SLP);
-      load_rows(a1, rec + RL + g * SLP);
+      load_rows(u, rec, g);
+      load_rows(rw_, rec + D, g);
+      load_rows(w, rec + 2 * D, g);
+      load_rows(au, rec + 3 * D, g);
+      load_rows(kk, rec + 4 * D, g);
+      const float vj = live ? rec[OFF_V + j] : 0.f;
+      const float alpha = rec[OFF_AB], beta = rec[OFF_AB + 1];
       float sa0 = 0.f, sa1 = 0.f, rw0 = 0.f, rw1 = 0.f;
 #pragma unroll
       for (int ii = 0; ii < SL; ii += 2) {
-        if (g * SL + ii < D) {
-          sa0 = fmaf(a0[ii], S[ii], sa0);
-          rw0 = fmaf(a1[ii], S[ii], rw0);
-        }
-        if (ii + 1 < SL && g * SL + ii + 1 < D) {
-          sa1 = fmaf(a0[ii + 1], S[ii + 1], sa1);
-          rw1 = fmaf(a1[ii + 1], S[ii + 1], rw1);
+        sa0 = fmaf(u[ii], S[ii], sa0);
+        rw0 = fmaf(rw_[ii], S[ii], rw0);
+        if (ii + 1 < SL) {
+          sa1 = fmaf(u[ii + 1], S[ii + 1], sa1);
+          rw1 = fmaf(rw_[ii + 1], S[ii + 1], rw1);
         }
       }
       float sa = sa0 + sa1, rw = rw0 + rw1;
-      sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-      rw += __shfl_xor_sync(0xffffffffu, rw, 1);
-      sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-      rw += __shfl_xor_sync(0xffffffffu, rw, 2);
-      const float vj = live ? rec[OFF_V + j] : 0.f;
-      if (live && g == 0)
-        p.out[(size_t)(t0 + tok) * ld_out + h * D + j] = fmaf(rec[OFF_AB + 1], vj, fmaf(-rec[OFF_AB], sa, rw));
-      load_rows(a0, rec + 2 * RL + g * SLP);
-      load_rows(a1, rec + 3 * RL + g * SLP);
 #pragma unroll
-      for (int ii = 0; ii < SL; ++ii)
-        if (g * SL + ii < D) S[ii] = fmaf(a0[ii], S[ii], -a1[ii] * sa);
-      load_rows(a0, rec + 4 * RL + g * SLP);
+      for (int ii = 0; ii < SL; ++ii) S[ii] = fmaf(kk[ii], vj, w[ii] * S[ii]);
 #pragma unroll
-      for (int ii = 0; ii < SL; ++ii)
-        if (g * SL + ii < D) S[ii] = fmaf(a0[ii], vj, S[ii]);
+      for (int o = 1; o < G; o <<= 1) {
+        sa += __shfl_xor_sync(0xffffffffu, sa, o);
+        rw += __shfl_xor_sync(0xffffffffu, rw, o);
+      }
+#pragma unroll
+      for (int ii = 0; ii < SL; ++ii) S[ii] = fmaf(-au[ii], sa, S[ii]);
+      if (live && g == 0) p.out[(size_t)(t0 + tok) * ld_out + h * D + j] = fmaf(beta, vj, fmaf(-alpha, sa, rw));
     }
   }
-  if (p.write) {
+  if (p.write && live) {
 #pragma unroll
-    for (int ii = 0; ii < SL; ++ii) {
-      const int i = g * SL + ii;
-      if (live && i < D) S_g[(size_t)i * D + j] = S[ii];
-    }
+    for (int ii = 0; ii < SL; ++ii) S_g[(size_t)row_of(g, ii) * D + j] = S[ii];
   }
 }
 
@@ -212,8 +205,7 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(float* __restrict__ 
       const float kk = k[at + i], rr = r[at + i];
       const float w = expf(-decay_rate * sigmoidf_(d[(size_t)t * ld_d + h * D + i] + to_f32(d_bias[h * D + i])));
       const float u = kk * inv, au = sigmoidf_(a[at + i] + to_f32(a_bias[h * D + i])) * u;
-      const int ir = at_row(i);
-      dst[ir] = u, dst[RL + ir] = rr * w, dst[2 * RL + ir] = w, dst[3 * RL + ir] = au, dst[4 * RL + ir] = kk;
+      dst[i] = u, dst[D + i] = rr * w, dst[2 * D + i] = w, dst[3 * D + i] = au, dst[4 * D + i] = kk;
       dst[OFF_V + i] = v[at + i];
       al = fmaf(rr, au, al);
       be = fmaf(rr, kk, be);
