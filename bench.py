@@ -366,7 +366,7 @@ def run_serve(folder, cfg, layers, requests, chunk, new_tokens, max_seq, lo=128,
 SOGULIX_SHAPES = {
     # width, feed-forward and vocabulary of the Qwen2.5 shape of the same name; mixers sized alike
     "0.5B": dict(heads=14, dim=64, rot_dim=32, vdim=64, kv_rank=256, q_rank=384, window=1024, decay_rank=64),
-    "1.5B": dict(heads=12, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768, window=2048, decay_rank=96),
+    "1.5B": dict(heads=12, dim=96, rot_dim=32, vdim=128, kv_rank=512, q_rank=768, window=2048, decay_rank=96),
 }
 
 
@@ -524,12 +524,22 @@ def kernel_points(shape, batch, ctx_len, prefill_tokens, pk):
         cache = bf(pages, PAGE_SIZE, W)
         q_cat = torch.randn(T, H, W, device=dev)
         sink = torch.zeros(H, device=dev)
-        ms = timed(lambda: ops.latent_attention(q_cat, cache, sink, ctx, ctx.groups[0], H, C, m["window"], 0.1),
-                   flush=flush)
         keys = [min(m["window"], p + n) for p, n in zip(pos0, q_lens)]
         pairs = sum(sum(min(m["window"], p + i + 1) for i in range(n)) for p, n in zip(pos0, q_lens))
-        record(f"latent_attention {label}", ms, nbytes=sum(keys) * W * 2 + T * H * (W * 4 + C * 2),
-               flops=2.0 * pairs * H * (W + C))
+        if label == "decode":
+            # single tokens read the latents as they are cached (absorbed form)
+            ms = timed(lambda: ops.latent_attention(q_cat, cache, sink, ctx, ctx.groups[0], H, C, m["window"], 0.1),
+                       flush=flush)
+            record("latent_attention decode", ms, nbytes=sum(keys) * W * 2 + T * H * (W * 4 + C * 2),
+                   flops=2.0 * pairs * H * (W + C))
+        elif ops.latent_plain_form_supported(torch.bfloat16, D, R, V):
+            # prompts: keys and values projected up for the step, then the tensor-core attention kernel
+            hd = ops.latent_head_size(D, R, V)
+            qp, outp, w_up = bf(T, H * hd), torch.empty(T, H * hd, dtype=torch.bfloat16, device=dev), bf(H * (D + V), C)
+            ms = timed(lambda: ops.latent_attention_plain_form(qp, cache, w_up, sink, ctx, ctx.groups[0], H, D, R, V, C,
+                                                               m["window"], 0.1, 16, outp), flush=flush)
+            record("latent_attention prefill (gather, project up, scatter, attention)", ms,
+                   flops=2.0 * sum(keys) * C * H * (D + V) + 4.0 * pairs * H * hd)
         # Qwen2's attention at the same heads (grouped 7:1 as in the shape) and head size
         nq, nkv = q["num_attention_heads"], q["num_key_value_heads"]
         d = q["hidden_size"] // nq

@@ -78,7 +78,7 @@ class ParallelStreamBlock(Block):
             return t if t.dtype == dtype else t.to(dtype)
 
         names = tuple(spec.get("scale_names") or ())
-        if names and len(names) != (2 if ffn is not None else 1) and len(names) != 2:
+        if names and len(names) < (2 if ffn is not None else 1):
             raise ValueError("parallel_stream: one scale per result")
         ones = None
         if not names:
