@@ -534,12 +534,12 @@ def kernel_points(shape, batch, ctx_len, prefill_tokens, pk):
                    flops=2.0 * pairs * H * (W + C))
         elif ops.latent_plain_form_supported(torch.bfloat16, D, R, V):
             # prompts: keys and values projected up for the step, then the tensor-core attention kernel
-            hd = ops.latent_head_size(D, R, V)
-            qp, outp, w_up = bf(T, H * hd), torch.empty(T, H * hd, dtype=torch.bfloat16, device=dev), bf(H * (D + V), C)
+            hsz = ops.latent_head_size(D, R, V)
+            qp, outp, w_up = bf(T, H * hsz), torch.empty(T, H * hsz, dtype=torch.bfloat16, device=dev), bf(H * (D + V), C)
             ms = timed(lambda: ops.latent_attention_plain_form(qp, cache, w_up, sink, ctx, ctx.groups[0], H, D, R, V, C,
                                                                m["window"], 0.1, 16, outp), flush=flush)
             record("latent_attention prefill (gather, project up, scatter, attention)", ms,
-                   flops=2.0 * sum(keys) * C * H * (D + V) + 4.0 * pairs * H * hd)
+                   flops=2.0 * sum(keys) * C * H * (D + V) + 4.0 * pairs * H * hsz)
         # Qwen2's attention at the same heads (grouped 7:1 as in the shape) and head size
         nq, nkv = q["num_attention_heads"], q["num_key_value_heads"]
         d = q["hidden_size"] // nq
