@@ -1,7 +1,8 @@
 // Row-wise operators for models whose residual stream is kept in 32-bit floats whatever the
 // storage type T of weights and activations is: embedding with a norm, RMS norms that read the
 // 32-bit stream (one or two at once, gain w or 1 + w), token shift with a per-request previous
-// row, the block's sum into the stream with per-channel scales, concatenation for a re-entry
+// row, the block's sum into the stream with per-channel scales (alone, or as the opening of the
+// next block's norms, as the 16-bit stream's add + norm kernel has it), concatenation for a re-entry
 // projection, and a soft cap on logits.  All arithmetic is 32-bit; T only says how weights are
 // stored and how outputs that feed a matrix product are rounded.
 #include "common.cuh"
@@ -130,6 +131,55 @@ __global__ void __launch_bounds__(kThreads) stream_add_kernel(float* __restrict_
   }
 }
 
+// ---- the block's sum and the norms that follow it, in one pass --------------------------------
+// v = x[src] + mult * (sa * a[src] + sb * b[src]) (a, b as above); without `rows` v replaces x[t]; then
+// out_a (32-bit) = v / rms(v) * (offset + wa) and out_b (T) = v / rms(v) * (offset + wb).  With `rows`,
+// output row t comes from row rows[t] and x is left as it is (the final norm at the wanted rows).
+template <typename T>
+__global__ void __launch_bounds__(kThreads) stream_add_norm_kernel(
+    float* __restrict__ out_a, T* __restrict__ out_b, float* __restrict__ x, const float* __restrict__ a, int a_splits,
+    const float* __restrict__ b, int b_splits, const T* __restrict__ sa, const T* __restrict__ sb,
+    long long split_stride, float mult, const T* __restrict__ wa, const T* __restrict__ wb,
+    const int* __restrict__ rows, int n_in, int hidden, float eps, float offset) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int src = t;
+  if (rows != nullptr) {
+    src = rows[t];
+    if (src < 0 || src >= n_in) {
+      if (threadIdx.x == 0) lab_set_error(LAB_ERR_ROW_RANGE);
+      return;
+    }
+  }
+  const size_t base = (size_t)src * hidden;
+  auto value = [&](int i) {
+    float va = 0.f;
+    for (int s = 0; s < a_splits; ++s) va += a[s * split_stride + base + i];
+    float total = va * to_f32(sa[i]);
+    if (b != nullptr) {
+      float vb = 0.f;
+      for (int s = 0; s < b_splits; ++s) vb += b[s * split_stride + base + i];
+      total += vb * to_f32(sb[i]);
+    }
+    return x[base + i] + mult * total;
+  };
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += kThreads) {
+    const float v = value(i);
+    if (rows == nullptr) x[base + i] = v;      // the same thread reads it back below
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += kThreads) {
+    const float v = (rows == nullptr ? x[base + i] : value(i)) * inv;
+    if (out_a != nullptr) out_a[(size_t)t * hidden + i] = v * (offset + to_f32(wa[i]));
+    if (out_b != nullptr) out_b[(size_t)t * hidden + i] = from_f32<T>(v * (offset + to_f32(wb[i])));
+  }
+}
+
 // ---- [x; x0] rounded to T -------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(kThreads) concat_kernel(T* __restrict__ out, const float* __restrict__ x,
@@ -205,6 +255,23 @@ LAB_EXPORT int lab_stream_add(float* x, const float* a, int a_splits, const floa
   else
     lab_launch(stream_add_kernel<__nv_bfloat16>, dim3(blocks_for(n)), dim3(kThreads), 0, stream, x, a, a_splits, b,
                b_splits, (const __nv_bfloat16*)sa, (const __nv_bfloat16*)sb, n, hidden, n, mult);
+  LAB_LAUNCH_CHECK();
+}
+
+LAB_EXPORT int lab_stream_add_norm(float* out_a, void* out_b, float* x, const float* a, int a_splits, const float* b,
+                                   int b_splits, const void* sa, const void* sb, float mult, const void* wa,
+                                   const void* wb, const int* rows, int n_out, int n_in, int hidden, float eps,
+                                   float offset, int dtype, cudaStream_t stream) {
+  if (n_out <= 0) return 0;
+  const long long stride = (long long)n_in * hidden;
+  if (dtype == LAB_F32)
+    lab_launch(stream_add_norm_kernel<float>, dim3(n_out), dim3(kThreads), 0, stream, out_a, (float*)out_b, x, a,
+               a_splits, b, b_splits, (const float*)sa, (const float*)sb, stride, mult, (const float*)wa,
+               (const float*)wb, rows, n_in, hidden, eps, offset);
+  else
+    lab_launch(stream_add_norm_kernel<__nv_bfloat16>, dim3(n_out), dim3(kThreads), 0, stream, out_a,
+               (__nv_bfloat16*)out_b, x, a, a_splits, b, b_splits, (const __nv_bfloat16*)sa, (const __nv_bfloat16*)sb,
+               stride, mult, (const __nv_bfloat16*)wa, (const __nv_bfloat16*)wb, rows, n_in, hidden, eps, offset);
   LAB_LAUNCH_CHECK();
 }
 

@@ -816,6 +816,34 @@ def stream_add(x: torch.Tensor, a: torch.Tensor, scale_a: torch.Tensor, b: torch
     return x
 
 
+def stream_add_norm(x: torch.Tensor, a: torch.Tensor, scale_a: torch.Tensor, b: torch.Tensor | None,
+                    scale_b: torch.Tensor | None, mult: float, eps: float, offset: float,
+                    weight_f32: torch.Tensor | None = None, weight: torch.Tensor | None = None,
+                    rows: torch.Tensor | None = None):
+    """`stream_add` and `norm_stream` in one pass over the rows: x += mult * (scale_a * a + scale_b * b), then
+    the norms of the sum.  With `rows` only those rows are formed and x is left as it is."""
+    _on_gpu(x, a, b, scale_a, scale_b, weight_f32, weight, rows)
+    n_in, hidden = x.shape
+    n_out = n_in if rows is None else rows.numel()
+    assert x.dtype == torch.float32 and x.is_contiguous() and (weight_f32 is not None or weight is not None)
+
+    def splits_of(t):
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.shape[-2:] == x.shape
+        return t.shape[0] if t.dim() == 3 else 1
+
+    sa = splits_of(a)
+    sb = splits_of(b) if b is not None else 0
+    wdt = scale_a.dtype
+    assert all(w is None or w.dtype == wdt for w in (scale_b, weight_f32, weight))
+    out_a = torch.empty((n_out, hidden), dtype=torch.float32, device=x.device) if weight_f32 is not None else None
+    out_b = torch.empty((n_out, hidden), dtype=wdt, device=x.device) if weight is not None else None
+    _check(lib("stream32").lab_stream_add_norm(
+        _ptr(out_a), _ptr(out_b), _ptr(x), _ptr(a), sa, _ptr(b), sb, _ptr(scale_a), _ptr(scale_b), ctypes.c_float(mult),
+        _ptr(weight_f32), _ptr(weight), _ptr(rows), n_out, n_in, hidden, ctypes.c_float(eps), ctypes.c_float(offset),
+        dtype_code(wdt), _stream()), "stream_add_norm")
+    return out_a, out_b
+
+
 def stream_concat(x: torch.Tensor, x0: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     """[x ; x0] row by row, rounded to `dtype`, for a projection that reads both."""
     _on_gpu(x, x0)

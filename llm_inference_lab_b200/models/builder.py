@@ -152,7 +152,10 @@ class CausalLM:
             entry = self.reentries.get(index)
             if entry is not None:
                 if pending is not None:
-                    raise ValueError("a re-entry follows a block that leaves part of its sum to the next norm")
+                    if not hasattr(pending, "add_to"):
+                        raise ValueError("a re-entry follows a block that leaves part of its sum to the next norm")
+                    pending.add_to(x)       # the re-entry reads the stream itself
+                    pending = None
                 with scoped_range("reentry"):
                     x = entry.forward(x, x0)
             view = caches[call.cache]

@@ -1,6 +1,9 @@
 """Arrangements of a mixer and a feed-forward around the residual stream."""
 from __future__ import annotations
 
+import dataclasses
+from typing import Optional
+
 import torch
 
 from ..kernels import ops
@@ -31,6 +34,20 @@ class PreNormBlock(Block):
 register_part("block", "prenorm", PreNormBlock)
 
 
+@dataclasses.dataclass
+class PendingSum:
+    """What a block still owes a 32-bit stream: x += mult * (scale_a * a + scale_b * b).  The next block's norms
+    (or the final norm) add it in their own pass; whoever needs the stream itself first calls `add_to`."""
+    a: torch.Tensor
+    scale_a: torch.Tensor
+    b: Optional[torch.Tensor]
+    scale_b: Optional[torch.Tensor]
+    mult: float
+
+    def add_to(self, x):
+        return ops.stream_add(x, self.a, self.scale_a, self.b, self.scale_b, self.mult)
+
+
 class ParallelStreamBlock(Block):
     """Mixer and feed-forward side by side on a 32-bit residual stream, each behind a norm of its own of
     the same x:
@@ -42,7 +59,8 @@ class ParallelStreamBlock(Block):
     h[t]) * mix per channel, h[t-1] taken before its own shift, zeros before a sequence's first token.  The
     last unshifted row of every request is fixed-size state of the block, beside the mixer's cache.  A layer
     may have no feed-forward.  The sum is 32-bit; both results arrive as 32-bit products (or split-K partial
-    products, summed here)."""
+    products, summed in order).  As in the pre-norm block, the sum that closes a block is fused with the
+    norms that open the next one: the block hands it on as `pending` (`PendingSum`)."""
     n_norms = 2
 
     @classmethod
@@ -93,15 +111,21 @@ class ParallelStreamBlock(Block):
                 raise ValueError("parallel_stream: both norms are rmsnorm_stream with the same constants")
 
     def forward(self, x, pending, ctx, cache):
-        if pending is not None:
-            raise ValueError("parallel_stream follows a block that leaves part of its sum to the next norm")
+        if pending is not None and not isinstance(pending, PendingSum):
+            raise ValueError("parallel_stream follows a block that leaves a sum of another kind to the next norm")
         n1 = self.norms[0]
         w2 = self.norms[1].weight if self.ffn is not None else None
         with scoped_range(self.mixer_range):
             if self.mix is not None:
-                normed, h2 = ops.norm_stream(x, n1.eps, n1.offset, weight_f32=n1.weight, weight=w2)
+                if pending is not None:
+                    normed, h2 = ops.stream_add_norm(x, pending.a, pending.scale_a, pending.b, pending.scale_b,
+                                                     pending.mult, n1.eps, n1.offset, weight_f32=n1.weight, weight=w2)
+                else:
+                    normed, h2 = ops.norm_stream(x, n1.eps, n1.offset, weight_f32=n1.weight, weight=w2)
                 h1 = ops.token_shift(normed, self.mix, cache.block_state, ctx, write=cache.write)
             else:
+                if pending is not None:
+                    pending.add_to(x)
                 h1 = ops.norm_stream(x, n1.eps, n1.offset, weight=n1.weight)[1]
                 h2 = ops.norm_stream(x, n1.eps, n1.offset, weight=w2)[1] if w2 is not None else None
             a = self.mixer.forward(h1, ctx, cache)
@@ -109,8 +133,7 @@ class ParallelStreamBlock(Block):
         if self.ffn is not None:
             with scoped_range(self.ffn_range):
                 f = self.ffn.forward(h2, ctx)
-        ops.stream_add(x, a, self.scale_mixer, f, self.scale_ffn, self.mult)
-        return x, None
+        return x, PendingSum(a, self.scale_mixer, f, self.scale_ffn, self.mult)
 
 
 register_part("block", "parallel_stream", ParallelStreamBlock)

@@ -46,9 +46,11 @@ class StreamRMSNorm(Norm):
         return ops.norm_stream(x, self.eps, self.offset, weight=self.weight, rows=rows)[1]
 
     def forward_add(self, x, delta, rows=None):
-        if delta is not None:
-            raise ValueError("a 32-bit stream takes its sums in the block, not in the next norm")
-        return self.forward(x, rows)
+        if delta is None:
+            return self.forward(x, rows)
+        # what the block before still owes the stream (`parts.block.PendingSum`): added here, in the norm's pass
+        return ops.stream_add_norm(x, delta.a, delta.scale_a, delta.b, delta.scale_b, delta.mult, self.eps, self.offset,
+                                   weight=self.weight, rows=rows)[1]
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -88,6 +88,18 @@ def test_stream_operators_against_numpy():
         y = x.clone()
         ops.stream_add(y, pb, w2, None, None, 2.0)
         assert np.abs(y.cpu().numpy() - (xd + 2.0 * pb.double().cpu().numpy() * w2.double().cpu().numpy())).max() < 1e-5
+        # the same sum as the opening of the next norms: bit-equal to the two steps, with and without a row gather
+        y = x.clone()
+        na, nb = ops.stream_add_norm(y, pa, w1, pb, w2, 0.3, 1e-5, 1.0, weight_f32=w2, weight=w1)
+        z = x.clone()
+        ops.stream_add(z, pa, w1, pb, w2, 0.3)
+        ra, rb = ops.norm_stream(z, 1e-5, 1.0, weight_f32=w2, weight=w1)
+        assert torch.equal(y, z) and torch.equal(na, ra) and torch.equal(nb, rb)
+        y = x.clone()
+        _, gb = ops.stream_add_norm(y, pb, w2, None, None, 2.0, 1e-5, 0.0, weight=w1, rows=rows)
+        z = x.clone()
+        ops.stream_add(z, pb, w2, None, None, 2.0)
+        assert torch.equal(y, x) and torch.equal(gb, ops.norm_stream(z, 1e-5, 0.0, weight=w1, rows=rows)[1])
         both = ops.stream_concat(x, y, dtype)
         assert both.shape == (T, 2 * H)
         assert torch.equal(both[:, :H], x.to(dtype)) and torch.equal(both[:, H:], y.to(dtype))
