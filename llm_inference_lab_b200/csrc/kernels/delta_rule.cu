@@ -111,6 +111,12 @@ __global__ void __launch_bounds__(NT) delta_rule_kernel(DeltaParams p) {
   const bool live = tid / G < CS;
   const int row0 = p.q_start[req], row1 = p.q_start[req + 1];
   const int slot = p.state_slot[req];
+  if (slot == -1) {      // a request of padding (length zero in a padded batch): zeros out, no state
+    const int jj = blockIdx.z * CS + tid / G;
+    if (tid / G < CS && tid % G == 0)
+      for (int t = row0; t < row1; ++t) p.out[(size_t)t * p.heads * D + h * D + jj] = 0.f;
+    return;
+  }
   if (slot < 0 || slot >= p.n_slots) {
     if (tid == 0) lab_set_error(LAB_ERR_PAGE_RANGE);
     return;

@@ -44,6 +44,7 @@ __global__ void __launch_bounds__(kThreads) latent_prep_kernel(T* __restrict__ c
   for (int i = threadIdx.x; i < Q; i += kThreads) cq[(size_t)t * Q + i] = from_f32<T>(row[i] * iq * to_f32(wq[i]));
   if (cache == nullptr) return;
   const long long slot = slots[t];
+  if (slot == -1) return;      // a row of padding: its latent goes nowhere
   if (slot < 0 || slot >= n_slots) {
     if (threadIdx.x == 0) lab_set_error(LAB_ERR_PAGE_RANGE);
     return;
@@ -176,6 +177,7 @@ struct LatentParams {
   const float* sink;      // [heads] or null
   const int* q_start;
   const int* pos0;
+  const int* kv_len;      // a request that holds nothing (padding of a padded batch) gets zeros
   const int* block_table;
   int bt_width, heads, C, W, page_size, num_pages, window, QT, HG;
   int below;              // > 0: only requests that bring fewer rows than this (others are served elsewhere)
@@ -197,6 +199,20 @@ __global__ void __launch_bounds__(kThreads) latent_attention_kernel(LatentParams
   const int C = p.C, W = p.W, KW = W + 1;
   const int h0 = blockIdx.z * p.HG, H = min(p.HG, p.heads - h0);     // this CTA's heads: h0 .. h0 + H - 1
   const int pairs = n * H;
+  if (p.kv_len[req] <= 0) {
+    if (p.splits > 1) {
+      // shares of nothing: the merge kernel writes the zeros
+      for (int i = threadIdx.x; i < pairs * (C + 2); i += kThreads) {
+        const int pair = i / (C + 2), c = i % (C + 2);
+        p.part[(((size_t)req * p.heads + h0 + pair) * p.splits + split) * (C + 2) + c] = c == 0 ? -INFINITY : 0.f;
+      }
+    } else {
+      T* zero = (T*)p.out;
+      for (int i = threadIdx.x; i < pairs * C; i += kThreads)
+        zero[((size_t)(first + (i / C) / H) * p.heads + h0 + (i / C) % H) * C + i % C] = from_f32<T>(0.f);
+    }
+    return;
+  }
   float* qs = smem;                                  // [QT * HG][W]
   float* keys = qs + (size_t)p.QT * p.HG * W;        // [kKeys][W + 1]
   float* acc = keys + kKeys * KW;                    // [QT * HG][C]
@@ -338,7 +354,7 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(T* __restrict__ out, 
       const float m = mine[(size_t)s * (C + 2)];
       if (m != -INFINITY) a = fmaf(expf(m - big), mine[(size_t)s * (C + 2) + 2 + c], a);
     }
-    out[((size_t)q_start[req] * heads + h) * C + c] = from_f32<T>(a / total);
+    out[((size_t)q_start[req] * heads + h) * C + c] = from_f32<T>(total > 0.f ? a / total : 0.f);
   }
 }
 
@@ -421,7 +437,8 @@ LAB_EXPORT int lab_latent_attention_rows(int heads, int C, int W, int max_q) {
 }
 
 LAB_EXPORT int lab_latent_attention(void* out, const float* q, const void* cache, const float* sink,
-                                    const int* q_start, const int* pos0, const int* block_table, int bt_width,
+                                    const int* q_start, const int* pos0, const int* kv_len, const int* block_table,
+                                    int bt_width,
                                     int n_requests, int max_q, int heads, int C, int W, int page_size, int num_pages,
                                     int window, float scale, int below, int splits, float* part, int dtype,
                                     cudaStream_t stream) {
@@ -431,7 +448,7 @@ LAB_EXPORT int lab_latent_attention(void* out, const float* q, const void* cache
   p.below = below;
   p.splits = splits < 1 ? 1 : splits;
   p.part = part;
-  p.out = out; p.q = q; p.cache = cache; p.sink = sink; p.q_start = q_start; p.pos0 = pos0;
+  p.out = out; p.q = q; p.cache = cache; p.sink = sink; p.q_start = q_start; p.pos0 = pos0; p.kv_len = kv_len;
   p.block_table = block_table; p.bt_width = bt_width; p.heads = heads; p.C = C; p.W = W; p.page_size = page_size;
   p.num_pages = num_pages; p.window = window; p.scale = scale;
   if (!attention_shape(heads, C, W, max_q, &p.QT, &p.HG)) return (int)cudaErrorInvalidValue;

@@ -89,6 +89,10 @@ __global__ void __launch_bounds__(kThreads) token_shift_kernel(T* __restrict__ o
   const int r = row_req[t];
   const int first = q_start[r], last = q_start[r + 1] - 1;
   const int slot = state_slot[r];
+  if (slot == -1) {      // a row of padding (a request of length zero in a padded batch): zeros, no state
+    for (int i = threadIdx.x; i < hidden; i += kThreads) out[(size_t)t * hidden + i] = from_f32<T>(0.f);
+    return;
+  }
   if (slot < 0 || slot >= n_slots) {
     if (threadIdx.x == 0) lab_set_error(LAB_ERR_PAGE_RANGE);
     return;

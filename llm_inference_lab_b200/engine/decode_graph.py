@@ -63,10 +63,12 @@ class DecodeGraphs:
     MAX_KEPT_BATCH = 1024
 
     def __init__(self, engine):
-        if engine.stateful:
-            # A mixer with state of its own may index it on the host, and the warm-up run before a
-            # capture would advance it twice: such models step eagerly.
-            raise ValueError("decode graphs do not serve models with fixed-size per-request state")
+        if not engine.decode_graph_capable:
+            # A mixer with state of its own may index it on the host: such models step eagerly.  Parts
+            # that keep their state on the device say so (`Part.decode_graph_safe`); the warm-up run
+            # before a capture advances their state, which is put back before the graph's first replay.
+            raise ValueError("decode graphs do not serve models with fixed-size per-request state that their parts "
+                             "may index on the host")
         self.engine = engine
         self.cached: dict[tuple, _Captured] = {}
         self.replays = 0
@@ -140,7 +142,7 @@ class DecodeGraphs:
             raise InvalidInput("no input ids given, and the previous step was not one of these requests")
         began = eng._begin(pairs, reserved)
         try:
-            cap = self._launch(pairs, B, tokens, temps, seeds, same_batch)
+            cap = self._launch(pairs, B, tokens, temps, seeds, same_batch, began[2])
         except Exception:
             eng._fail(began)
             raise
@@ -160,7 +162,7 @@ class DecodeGraphs:
             return (buf, event, B)
         return cap.tokens[:B]
 
-    def _launch(self, pairs, B, tokens, temps, seeds, same_batch) -> _Captured:
+    def _launch(self, pairs, B, tokens, temps, seeds, same_batch, saved_state=None) -> _Captured:
         """Uploads the step's metadata into the buffers of the graph that serves it (captured now if
         it is new) and replays it."""
         eng = self.engine
@@ -220,6 +222,8 @@ class DecodeGraphs:
                 self._run(cap, ctx)
             torch.cuda.current_stream().wait_stream(side)
             cap.tokens.copy_(saved)
+            for state, slots, rows in saved_state or ():
+                state[slots] = rows          # the warm-up run advanced fixed-size state: back to the step's start
             if self._pool is None:
                 self._pool = torch.cuda.graph_pool_handle()
             before = ops.COUNTER.launches

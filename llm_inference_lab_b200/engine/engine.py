@@ -122,6 +122,11 @@ class Engine:
         # every tensor of fixed-size per-request state, the mixers' and the blocks' own
         self.state_tensors = [t for v in self.views for t in (v.state, v.block_state) if t is not None]
         self.stateful = bool(self.state_tensors)
+        # Decode steps of a stateful model may run from CUDA graphs if every block and mixer says so
+        # (`Part.decode_graph_safe`); models without fixed-size state always may.
+        self.decode_graph_capable = not self.stateful or all(
+            getattr(b, "decode_graph_safe", False) and getattr(b.mixer, "decode_graph_safe", False)
+            for b in model.blocks)
         self.max_blocks = -(-self.max_seq_len // self.page_size)
         self.stats = EngineStats()
         self._staging = [self._new_staging() for _ in range(3)]

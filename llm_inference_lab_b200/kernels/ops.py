@@ -991,7 +991,7 @@ def latent_attention(q_cat: torch.Tensor, cache: torch.Tensor, sink: torch.Tenso
             part = torch.empty((ctx.n_requests * heads * splits * (kv_rank + 2),), dtype=torch.float32,
                                device=cache.device)
     _check(L.lab_latent_attention(_ptr(out), _ptr(q_cat), _ptr(cache), _ptr(sink), _ptr(ctx.q_start), _ptr(ctx.pos0),
-                                  _ptr(table), table.shape[1], ctx.n_requests, max_q, heads, kv_rank, width,
+                                  _ptr(ctx.kv_len), _ptr(table), table.shape[1], ctx.n_requests, max_q, heads, kv_rank, width,
                                   page_size, num_pages, window, ctypes.c_float(scale), int(below), splits, _ptr(part),
                                   dtype_code(cache.dtype), _stream()), "latent_attention", 2 if splits > 1 else 1)
     return out

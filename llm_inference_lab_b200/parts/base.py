@@ -78,6 +78,11 @@ class CacheView:
 
 class Part:
     kind = ""
+    # True: a decode step of this part may be captured into a CUDA graph although the model keeps fixed-size
+    # state: the part reads and writes its state through the step's device arrays only (never by host
+    # indices), skips rows of padding (state slot -1, page slot -1, length 0), and a run of the step that is
+    # repeated after the state was put back gives the same result.
+    decode_graph_safe = False
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> list[TensorSpec]:
@@ -150,6 +155,7 @@ class PositionEncoding(Part):
 
 class Block:
     kind = ""
+    decode_graph_safe = False     # as `Part.decode_graph_safe`, for an arrangement with state of its own
 
     @classmethod
     def tensors(cls, spec: Optional[PartSpec]) -> list[TensorSpec]:

@@ -61,6 +61,8 @@ class ParallelStreamBlock(Block):
     may have no feed-forward.  The sum is 32-bit; both results arrive as 32-bit products (or split-K partial
     products, summed in order).  As in the pre-norm block, the sum that closes a block is fused with the
     norms that open the next one: the block hands it on as `pending` (`PendingSum`)."""
+    decode_graph_safe = True
+
     n_norms = 2
 
     @classmethod

@@ -24,6 +24,8 @@ class GeneralDelta(Mixer):
     The six matrices that read h are concatenated at load time: one product.  Everything that enters the
     recurrence besides the products themselves is formed in 32-bit inside the recurrence kernel
     (`csrc/kernels/delta_rule.cu`), which serves prompts' portions and single decoded tokens alike."""
+    decode_graph_safe = True
+
 
     NAMES = ("r", "k", "v", "g", "a")
 

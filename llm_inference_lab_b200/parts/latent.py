@@ -22,6 +22,8 @@ class LatentAttention(Mixer):
     p sees the keys j with 0 <= p - j < window), `sink` (a learned number per head that joins the softmax's
     denominator, unscaled, without key or value), rotary base and the number of rotated entries `rot_dims`
     of the rotated part (entry i pairs with i + rot_dims / 2), `scale`."""
+    decode_graph_safe = True
+
 
     @classmethod
     def tensors(cls, spec: PartSpec):

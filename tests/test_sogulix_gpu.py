@@ -448,6 +448,40 @@ def test_greedy_generation_through_the_scheduler(tmp_path, name):
     assert llm.engine.cache.live_requests == 0
 
 
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16")])
+def test_decode_steps_from_cuda_graphs(tmp_path, name, dtype):
+    """Decode steps of a model with fixed-size state replayed from CUDA graphs (its parts keep the state on the
+    device): batches padded with requests of length zero, a batch that shrinks from graph to graph as requests
+    finish, the state put back after the warm-up run of every capture, lookahead.  32-bit: the plain model's
+    tokens; bfloat16: the tokens of the same engine stepping eagerly."""
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.kernels import ops
+    from llm_inference_lab_b200.sampling import SamplingConfig
+    cfg, opt = SMALL[name]
+    folder = make_model_folder(str(tmp_path / "m"), cfg, 23, dtype, std=0.08, scales=SPREAD)
+    rng = np.random.default_rng(5)
+    prompts = [[int(t) for t in rng.integers(0, cfg["vocab"], size=n)] for n in (7, 30, 2, 19, 11)]
+    sampling = [SamplingConfig(max_new_tokens=n, ignore_eos=True) for n in (20, 5, 14, 9, 17)]
+
+    def run(graph):
+        llm = LLM(folder, dtype, page_size=opt["page_size"], kv_tokens=1024, max_requests=8, max_batch_tokens=64,
+                  max_seq_len=128, device="cuda:0", cuda_graph=graph)
+        assert llm.cuda_graph == graph
+        out = [r.tokens for r in llm.generate(prompts, sampling)]
+        ops.take_device_errors()
+        assert llm.engine.cache.live_requests == 0
+        if graph:
+            assert llm.graphs.replays >= 10 and llm.graphs.captures >= 3
+        return out
+
+    got = run(True)
+    if dtype == "float32":
+        pcfg, w = ps.read_folder(folder)
+        assert got == [ps.greedy(pcfg, w, p, s.max_new_tokens) for p, s in zip(prompts, sampling)]
+    else:
+        assert got == run(False)
+
+
 def test_command_line_generates(tmp_path):
     import json
     import subprocess
