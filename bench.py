@@ -452,6 +452,15 @@ def model_points(folder, batch, prompt_len, prefill_tokens, decode_steps):
     ms = timed(decode, repeats=3) / decode_steps
     out["decode_ms_per_step"], out["decode_tok_s"] = round(ms, 4), round(batch / (ms / 1e3), 1)
     ops.take_device_errors()
+    for r in range(batch):
+        engine.close(r)
+    if engine.decode_graph_capable:
+        # the same steps replayed from CUDA graphs, the picked ids fed forward on the device
+        from llm_inference_lab_b200.engine.decode_graph import DecodeGraphs
+        gms, launches, _ = median_region(run_decode(engine, DecodeGraphs(engine), batch, decode_steps, 5, rng, repeats=3))
+        out["decode_graph_ms_per_step"] = round(gms / decode_steps, 4)
+        out["decode_graph_tok_s"] = round(batch * decode_steps / (gms / 1e3), 1)
+        out["decode_graph_launches_per_step"] = launches // decode_steps
     del engine
     torch.cuda.empty_cache()
     return out

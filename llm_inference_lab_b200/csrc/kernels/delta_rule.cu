@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(float* __restrict__ 
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int h = warp; h < heads; h += 8) {
+  for (int h = blockIdx.y * 8 + warp; h < heads; h += 8 * gridDim.y) {
     const size_t at = (size_t)t * ld + h * D;
     float ss = 0.f;
     for (int i = lane; i < D; i += 32) ss += k[at + i] * k[at + i];
@@ -231,7 +231,7 @@ __global__ void __launch_bounds__(256) delta_finish_kernel(T* __restrict__ out, 
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int h = warp; h < heads; h += 8) {
+  for (int h = blockIdx.y * 8 + warp; h < heads; h += 8 * gridDim.y) {
     const float* o = raw + ((size_t)t * heads + h) * D;
     float ss = 0.f;
     for (int i = lane; i < D; i += 32) ss += o[i] * o[i];
@@ -277,22 +277,25 @@ LAB_EXPORT int lab_delta_rule(void* out, float* scratch, const float* r, const f
   p.state_slot = state_slot; p.heads = heads; p.n_slots = n_slots; p.write = write;
   const size_t smem = sizeof(DeltaShared);
   const dim3 grid(heads, n_requests, NS);
+  // the two kernels that are parallel over tokens: a warp per (token, head); with few tokens the heads
+  // spread over CTAs as well
+  const dim3 per_token(tokens, tokens >= 512 ? 1 : (heads + 7) / 8);
   cudaError_t e;
   if (dtype == LAB_F32) {
     e = cudaFuncSetAttribute(delta_rule_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    lab_launch(delta_prepare_kernel<float>, dim3(tokens), dim3(256), 0, stream, records, tokens, r, k, v, a, ld, d,
+    lab_launch(delta_prepare_kernel<float>, per_token, dim3(256), 0, stream, records, tokens, r, k, v, a, ld, d,
                ld_d, (const float*)d_bias, (const float*)a_bias, heads, decay_rate);
     lab_launch(delta_rule_kernel<float>, grid, dim3(NT), smem, stream, p);
-    lab_launch(delta_finish_kernel<float>, dim3(tokens), dim3(256), 0, stream, (float*)out, (const float*)raw, g, ld,
+    lab_launch(delta_finish_kernel<float>, per_token, dim3(256), 0, stream, (float*)out, (const float*)raw, g, ld,
                (const float*)norm_w, heads, eps);
   } else {
     e = cudaFuncSetAttribute(delta_rule_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    lab_launch(delta_prepare_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, records, tokens, r, k, v, a,
+    lab_launch(delta_prepare_kernel<__nv_bfloat16>, per_token, dim3(256), 0, stream, records, tokens, r, k, v, a,
                ld, d, ld_d, (const __nv_bfloat16*)d_bias, (const __nv_bfloat16*)a_bias, heads, decay_rate);
     lab_launch(delta_rule_kernel<__nv_bfloat16>, grid, dim3(NT), smem, stream, p);
-    lab_launch(delta_finish_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (__nv_bfloat16*)out,
+    lab_launch(delta_finish_kernel<__nv_bfloat16>, per_token, dim3(256), 0, stream, (__nv_bfloat16*)out,
                (const float*)raw, g, ld, (const __nv_bfloat16*)norm_w, heads, eps);
   }
   LAB_LAUNCH_CHECK();

@@ -87,6 +87,49 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(OutT* __restrict__ out,
   }
 }
 
+// Per-head products for few tokens (a decode step): out[t, h, n] = sum_k w[h, n, k] * x[t, h, k].  A warp
+// forms one output column for every token: it reads the weight row once, lanes over k, and finishes each
+// token's sum with a shuffle tree; the tokens' inputs of the head wait in shared memory.  The 64 x 64 tiles
+// above walk K in steps of 16 behind a barrier each, which costs a memory latency per step.
+constexpr int HF_TOKENS = 16;
+template <typename T, typename OutT>
+__global__ void __launch_bounds__(256) gemm_heads_few_kernel(OutT* __restrict__ out, const T* __restrict__ x,
+                                                             const T* __restrict__ w, int M, int N, int K, int ldx,
+                                                             int ldo, long long head_x, long long head_o) {
+  extern __shared__ float hf_x[];      // [M][K]
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < M * K; i += 256) hf_x[i] = to_f32<T>(x[(size_t)(i / K) * ldx + h * head_x + i % K]);
+  __syncthreads();
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= N) return;
+  const T* row = w + ((size_t)h * N + n) * K;
+  float acc[HF_TOKENS];
+#pragma unroll
+  for (int t = 0; t < HF_TOKENS; ++t) acc[t] = 0.f;
+  for (int k = lane; k < K; k += 32) {
+    const float wv = to_f32<T>(row[k]);
+#pragma unroll
+    for (int t = 0; t < HF_TOKENS; ++t)
+      if (t < M) acc[t] = fmaf(wv, hf_x[t * K + k], acc[t]);
+  }
+#pragma unroll
+  for (int t = 0; t < HF_TOKENS; ++t) {
+    if (t >= M) break;
+    const float v = warp_sum(acc[t]);
+    if (lane == 0) out[(size_t)t * ldo + h * head_o + n] = from_f32<OutT>(v);
+  }
+}
+
+template <typename T, typename OutT>
+int launch_heads_few(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, int heads,
+                     long long head_x, long long head_o, cudaStream_t stream) {
+  return (int)lab_launch(gemm_heads_few_kernel<T, OutT>, dim3((N + 7) / 8, heads), dim3(256),
+                         sizeof(float) * (size_t)M * K, stream, (OutT*)out, (const T*)x, (const T*)w, M, N, K, ldx, ldo,
+                         head_x, head_o);
+}
+
 template <typename T, typename OutT>
 int launch(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx, int ldo, int gated,
            cudaStream_t stream, int batch = 1, long long batch_x = 0, long long batch_w = 0, long long batch_o = 0) {
@@ -115,6 +158,13 @@ LAB_EXPORT int lab_gemm_plain_batched(void* out, const void* x, const void* w, i
                                       int out_f32, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || batch <= 0) return 0;
   if (batch > 65535) return (int)cudaErrorInvalidValue;
+  if (M <= HF_TOKENS && (size_t)M * K * sizeof(float) <= 48 * 1024 && batch_w == (long long)N * K) {
+    if (dtype == LAB_F32)
+      return launch_heads_few<float, float>(out, x, w, M, N, K, ldx, ldo, batch, batch_x, batch_o, stream);
+    if (out_f32)
+      return launch_heads_few<__nv_bfloat16, float>(out, x, w, M, N, K, ldx, ldo, batch, batch_x, batch_o, stream);
+    return launch_heads_few<__nv_bfloat16, __nv_bfloat16>(out, x, w, M, N, K, ldx, ldo, batch, batch_x, batch_o, stream);
+  }
   if (dtype == LAB_F32)
     return launch<float, float>(out, x, w, nullptr, M, N, K, ldx, ldo, 0, stream, batch, batch_x, batch_w, batch_o);
   if (out_f32)

@@ -341,18 +341,33 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(T* __restrict__ out, 
   const int rows = q_start[req + 1] - q_start[req];
   if (rows <= 0 || (below > 0 && rows >= below)) return;
   const float* mine = part + ((size_t)req * heads + h) * splits * (C + 2);
-  float big = -INFINITY;
-  for (int s = 0; s < splits; ++s) big = fmaxf(big, mine[(size_t)s * (C + 2)]);
-  float total = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float m = mine[(size_t)s * (C + 2)];
-    total += m == -INFINITY ? 0.f : expf(m - big) * mine[(size_t)s * (C + 2) + 1];
+  // every share's weight once, in shared memory (a loop of dependent loads costs a latency per share)
+  __shared__ float weight[64];
+  if (threadIdx.x < 64) {
+    const float m = threadIdx.x < splits ? mine[(size_t)threadIdx.x * (C + 2)] : -INFINITY;
+    float big = m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, o));
+    weight[threadIdx.x] = big;      // the warp's maximum for now
   }
+  __syncthreads();
+  const float big = fmaxf(weight[0], weight[32]);
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    const float m = threadIdx.x < splits ? mine[(size_t)threadIdx.x * (C + 2)] : -INFINITY;
+    weight[threadIdx.x] = m == -INFINITY ? 0.f : expf(m - big);
+  }
+  __syncthreads();
+  float total = 0.f;
+  for (int s = 0; s < splits; ++s) total += weight[s] * mine[(size_t)s * (C + 2) + 1];
   for (int c = threadIdx.x; c < C; c += 128) {
     float a = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float m = mine[(size_t)s * (C + 2)];
-      if (m != -INFINITY) a = fmaf(expf(m - big), mine[(size_t)s * (C + 2) + 2 + c], a);
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = s0 + j < splits ? mine[(size_t)(s0 + j) * (C + 2) + 2 + c] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a = fmaf(s0 + j < splits ? weight[s0 + j] : 0.f, v[j], a);
     }
     out[((size_t)q_start[req] * heads + h) * C + c] = from_f32<T>(total > 0.f ? a / total : 0.f);
   }

@@ -11,6 +11,20 @@ namespace {
 
 constexpr int kThreads = 256;
 
+// Sum of split-K partial products p[s * stride + at], s ascending.  The loads of eight splits are issued
+// before the first add: a loop whose every load feeds the next add runs one memory latency per split.
+__device__ __forceinline__ float sum_splits(const float* __restrict__ p, int splits, long long stride, size_t at) {
+  float total = 0.f;
+  for (int s0 = 0; s0 < splits; s0 += 8) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = s0 + j < splits ? p[(s0 + j) * stride + at] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) total += v[j];
+  }
+  return total;
+}
+
 // ---- embedding + norm ---------------------------------------------------------------------
 // out[t] = table[id_t] / rms(table[id_t]) * (offset + w)
 template <typename T>
@@ -123,14 +137,8 @@ __global__ void __launch_bounds__(kThreads) stream_add_kernel(float* __restrict_
   pdl_wait();
   for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += (long long)gridDim.x * kThreads) {
     const int c = (int)(i % hidden);
-    float va = 0.f;
-    for (int s = 0; s < a_splits; ++s) va += a[s * split_stride + i];
-    float total = va * to_f32(sa[c]);
-    if (b != nullptr) {
-      float vb = 0.f;
-      for (int s = 0; s < b_splits; ++s) vb += b[s * split_stride + i];
-      total += vb * to_f32(sb[c]);
-    }
+    float total = sum_splits(a, a_splits, split_stride, (size_t)i) * to_f32(sa[c]);
+    if (b != nullptr) total += sum_splits(b, b_splits, split_stride, (size_t)i) * to_f32(sb[c]);
     x[i] += mult * total;
   }
 }
@@ -140,7 +148,7 @@ __global__ void __launch_bounds__(kThreads) stream_add_kernel(float* __restrict_
 // out_a (32-bit) = v / rms(v) * (offset + wa) and out_b (T) = v / rms(v) * (offset + wb).  With `rows`,
 // output row t comes from row rows[t] and x is left as it is (the final norm at the wanted rows).
 template <typename T>
-__global__ void __launch_bounds__(kThreads) stream_add_norm_kernel(
+__global__ void __launch_bounds__(1024) stream_add_norm_kernel(
     float* __restrict__ out_a, T* __restrict__ out_b, float* __restrict__ x, const float* __restrict__ a, int a_splits,
     const float* __restrict__ b, int b_splits, const T* __restrict__ sa, const T* __restrict__ sb,
     long long split_stride, float mult, const T* __restrict__ wa, const T* __restrict__ wb,
@@ -159,25 +167,19 @@ __global__ void __launch_bounds__(kThreads) stream_add_norm_kernel(
   }
   const size_t base = (size_t)src * hidden;
   auto value = [&](int i) {
-    float va = 0.f;
-    for (int s = 0; s < a_splits; ++s) va += a[s * split_stride + base + i];
-    float total = va * to_f32(sa[i]);
-    if (b != nullptr) {
-      float vb = 0.f;
-      for (int s = 0; s < b_splits; ++s) vb += b[s * split_stride + base + i];
-      total += vb * to_f32(sb[i]);
-    }
+    float total = sum_splits(a, a_splits, split_stride, base + i) * to_f32(sa[i]);
+    if (b != nullptr) total += sum_splits(b, b_splits, split_stride, base + i) * to_f32(sb[i]);
     return x[base + i] + mult * total;
   };
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += kThreads) {
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     const float v = value(i);
     if (rows == nullptr) x[base + i] = v;      // the same thread reads it back below
     ss += v * v;
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
-  for (int i = threadIdx.x; i < hidden; i += kThreads) {
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     const float v = (rows == nullptr ? x[base + i] : value(i)) * inv;
     if (out_a != nullptr) out_a[(size_t)t * hidden + i] = v * (offset + to_f32(wa[i]));
     if (out_b != nullptr) out_b[(size_t)t * hidden + i] = from_f32<T>(v * (offset + to_f32(wb[i])));
@@ -268,12 +270,14 @@ LAB_EXPORT int lab_stream_add_norm(float* out_a, void* out_b, float* x, const fl
                                    float offset, int dtype, cudaStream_t stream) {
   if (n_out <= 0) return 0;
   const long long stride = (long long)n_in * hidden;
+  // few rows (a decode step): an element a thread, so that a row's loads are all in flight at once
+  const int threads = n_out <= 64 ? (hidden >= 1024 ? 1024 : (hidden + 31) / 32 * 32) : kThreads;
   if (dtype == LAB_F32)
-    lab_launch(stream_add_norm_kernel<float>, dim3(n_out), dim3(kThreads), 0, stream, out_a, (float*)out_b, x, a,
+    lab_launch(stream_add_norm_kernel<float>, dim3(n_out), dim3(threads), 0, stream, out_a, (float*)out_b, x, a,
                a_splits, b, b_splits, (const float*)sa, (const float*)sb, stride, mult, (const float*)wa,
                (const float*)wb, rows, n_in, hidden, eps, offset);
   else
-    lab_launch(stream_add_norm_kernel<__nv_bfloat16>, dim3(n_out), dim3(kThreads), 0, stream, out_a,
+    lab_launch(stream_add_norm_kernel<__nv_bfloat16>, dim3(n_out), dim3(threads), 0, stream, out_a,
                (__nv_bfloat16*)out_b, x, a, a_splits, b, b_splits, (const __nv_bfloat16*)sa, (const __nv_bfloat16*)sb,
                stride, mult, (const __nv_bfloat16*)wa, (const __nv_bfloat16*)wb, rows, n_in, hidden, eps, offset);
   LAB_LAUNCH_CHECK();

@@ -983,10 +983,10 @@ def latent_attention(q_cat: torch.Tensor, cache: torch.Tensor, sink: torch.Tenso
     splits, part = 1, None
     if max_q == 1:
         # single tokens: the keys' tiles (32 keys each) of a request are shared out over CTAs while the launch
-        # stays within two rounds of the SMs, four tiles a share at least; a merge kernel sums the shares
+        # stays within two rounds of the SMs, two tiles a share at least; a merge kernel sums the shares
         span = min(ctx.max_kv_len, window) if window > 0 else ctx.max_kv_len
         ctas = ctx.n_requests * -(-heads // max(1, L.lab_latent_attention_heads(heads, kv_rank, width, 1)))
-        splits = int(max(1, min(-(-span // 128), (2 * sm_count()) // max(ctas, 1), 64)))
+        splits = int(max(1, min(-(-span // 64), (2 * sm_count()) // max(ctas, 1), 64)))
         if splits > 1:
             part = torch.empty((ctx.n_requests * heads * splits * (kv_rank + 2),), dtype=torch.float32,
                                device=cache.device)
