@@ -12,7 +12,8 @@
 // Formulas: rust/engine/src/runner/model/qwen2/kernels.rs:702-853 (scores scaled by
 // 1/sqrt(d), mask key <= query, online softmax with max/sum/accumulator in 32-bit,
 // o = acc / sum), 898-942 (merge of partial softmax states).  The window (keys with
-// query - key < window) is this engine's addition.
+// query - key < window; a negative `window` means chunks of that many positions, see
+// `lab_first_key`) is this engine's addition.
 #include "common.cuh"
 
 namespace {
@@ -38,7 +39,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_plain_kernel(
   for (int i = threadIdx.x; i < d; i += blockDim.x) qs[i] = to_f32<T>(q[(size_t)t * q_stride + (size_t)h * d + i]);
   __syncthreads();
 
-  const int first = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int first = lab_first_key(p, window);
   float m = -INFINITY, l = 0.f, acc[MAX_DPL];
 #pragma unroll
   for (int i = 0; i < MAX_DPL; ++i) acc[i] = 0.f;

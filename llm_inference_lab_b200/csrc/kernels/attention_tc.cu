@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
 
   const int last_row = min(r0 + PF_BM, ql) - 1;
   const int hi_all = p0 + last_row;
-  const int lo_all = window > 0 ? max(0, p0 + r0 - window + 1) : 0;
+  const int lo_all = lab_first_key(p0 + r0, window);
   const int t_first = lo_all / PF_BN, t_last = hi_all / PF_BN;
 
   auto issue = [&](int t, int stage) {
@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
     const int row = r0 + warp * 16 + (lane >> 2) + 8 * r;
     const int pos = p0 + row;
     hi[r] = row < ql ? pos : -1;
-    lo[r] = window > 0 ? max(0, pos - window + 1) : 0;
+    lo[r] = lab_first_key(pos, window);
   }
   float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   if (sink != nullptr) {
@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
       // A tile that lies wholly before the warp's first row (and inside every row's window) needs no mask.
       const int first_row = r0 + warp * 16;
       const bool all_visible = first_row + 15 < ql && t * PF_BN + PF_BN - 1 <= p0 + first_row &&
-                               (window == 0 || t * PF_BN >= p0 + first_row + 15 - window + 1);
+                               (window == 0 || t * PF_BN >= lab_first_key(p0 + first_row + 15, window));
       tile_step<PF_BN>(qf, kd, kd + PF_TILE_BYTES, o, m, l, t * PF_BN, lo, hi, scale_log2, lane, all_visible);
     }
     __syncthreads();  // the stage is refilled by the next iteration's prefetch
@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
   const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y - kvh * m_tiles;
   const int split = blockIdx.x;
   const int kvl = kv_len_arr[b];
-  const int first = window > 0 ? max(0, kvl - window) : 0;
+  const int first = lab_first_key(kvl - 1, window);
   const int* bt = block_table + (size_t)b * max_blocks;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int head0 = kvh * group + mt * 16;           // first query head of this CTA

@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int last_row = min(r0 + BM, ql) - 1;
   const int hi_all = p0 + last_row;                                    // last key any row sees
-  const int lo_all = window > 0 ? max(0, p0 + r0 - window + 1) : 0;    // first key any row sees
+  const int lo_all = lab_first_key(p0 + r0, window);                  // first key any row sees
   const int t_first = lo_all / BN, t_last = hi_all / BN;
   const int n_tiles = t_last - t_first + 1;
 
@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
     const int pos = p0 + r0 + row;                  // absolute position of this row's query
     const bool row_valid = r0 + row < ql;
     const int hi = row_valid ? pos : -1;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = lab_first_key(pos, window);
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     {
       // O accumulates in tensor memory over all tiles, relative to a reference maximum m_ref per row

@@ -47,6 +47,16 @@ __device__ __forceinline__ void rope_rotate(float lo, float hi, float cs, float 
   out_hi = __fmaf_rn(hi, cs, __fmul_rn(lo, sn));
 }
 
+// The first key a query at position `pos` sees, by the mask's span: 0, every key from 0 on; a positive
+// span, the last `span` keys (a sliding window); a negative one, the keys of the query's own chunk of
+// -span positions, chunks counted from position 0 of the sequence.  The last key is `pos` in every case.
+// Monotonic in `pos`, which the tile loops of the attention kernels rely on.
+__host__ __device__ __forceinline__ int lab_first_key(int pos, int span) {
+  if (span > 0) return pos - span + 1 > 0 ? pos - span + 1 : 0;
+  if (span < 0) return pos < 0 ? 0 : (pos / (-span)) * (-span);
+  return 0;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 // 2^x by the hardware approximation (relative error about 2^-22; -inf gives 0).
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -71,6 +81,13 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, int rank) {
 }
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+// The tanh form of GELU: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  One spelling for the
+// activation kernel and the matrix products' epilogues, so that all of them round alike.
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  const float inner = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
+  return 0.5f * z * (1.0f + tanhf(inner));
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {

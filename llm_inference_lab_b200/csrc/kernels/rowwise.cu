@@ -457,6 +457,27 @@ LAB_EXPORT int lab_rope_kv_write(void* qkv, int row_stride, const float* partial
 }
 
 // ----------------------------------------------------------------------------------------
+// GELU (tanh form) in place, for feed-forwards whose product kernel does not apply it itself.
+// ----------------------------------------------------------------------------------------
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(256) gelu_tanh_kernel(T* __restrict__ x, long long n) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long long)gridDim.x * 256)
+    x[i] = from_f32<T>(gelu_tanh_f(to_f32<T>(x[i])));
+}
+}  // namespace
+
+LAB_EXPORT int lab_gelu_tanh(void* x, long long n, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  if (dtype == LAB_F32) lab_launch(gelu_tanh_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, n);
+  else lab_launch(gelu_tanh_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)x, n);
+  LAB_LAUNCH_CHECK();
+}
+
+// ----------------------------------------------------------------------------------------
 // A copy from pinned host memory to the device on a stream: what a step's metadata takes.  Called
 // directly, it costs the host a fraction of what the same copy costs through a tensor library.
 // ----------------------------------------------------------------------------------------

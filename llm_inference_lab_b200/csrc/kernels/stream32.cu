@@ -1,6 +1,7 @@
 // Row-wise operators for models whose residual stream is kept in 32-bit floats whatever the
 // storage type T of weights and activations is: embedding with a norm, RMS norms that read the
-// 32-bit stream (one or two at once, gain w or 1 + w), token shift with a per-request previous
+// 32-bit stream (one or two at once, gain w or 1 + w), embedding with a learned position, the sum
+// x += norm(product) of blocks that norm a sublayer's output, token shift with a per-request previous
 // row, the block's sum into the stream with per-channel scales (alone, or as the opening of the
 // next block's norms, as the 16-bit stream's add + norm kernel has it), concatenation for a re-entry
 // projection, and a soft cap on logits.  All arithmetic is 32-bit; T only says how weights are
@@ -186,6 +187,79 @@ __global__ void __launch_bounds__(1024) stream_add_norm_kernel(
   }
 }
 
+// ---- embedding + learned position ---------------------------------------------------------
+// out[t] = table[id_t] + positions[p_t] as a 32-bit row.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) embed_position_kernel(float* __restrict__ out,
+                                                                  const T* __restrict__ table,
+                                                                  const T* __restrict__ pos_table,
+                                                                  const int* __restrict__ ids,
+                                                                  const int* __restrict__ positions, int hidden,
+                                                                  int vocab, int max_positions) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int id = ids[t], p = positions[t];
+  id = min(max(id, 0), vocab - 1);
+  if (p >= max_positions && threadIdx.x == 0) lab_set_error(LAB_ERR_ROW_RANGE);
+  p = min(max(p, 0), max_positions - 1);
+  const T* row = table + (size_t)id * hidden;
+  const T* prow = pos_table + (size_t)p * hidden;
+  for (int i = threadIdx.x; i < hidden; i += kThreads)
+    out[(size_t)t * hidden + i] = to_f32(row[i]) + to_f32(prow[i]);
+}
+
+// ---- x += norm(product): the sum that closes a sublayer whose *output* is normed ----------------
+// y = a[t] (+ bias), a a 32-bit product [tokens, hidden] or split-K partial products summed in ascending
+// order; x[t] += y / rms(y) * w; and (if asked) the new x[t] rounded to T, for the product that reads
+// the stream next.
+template <typename T>
+__global__ void __launch_bounds__(1024) stream_norm_add_kernel(float* __restrict__ x, T* __restrict__ copy,
+                                                               const float* __restrict__ a, int a_splits,
+                                                               long long split_stride, const T* __restrict__ bias,
+                                                               const T* __restrict__ w, int hidden, float eps) {
+  __shared__ float scratch[32];
+  extern __shared__ float row[];      // [hidden]: the product's row, summed once
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const size_t base = (size_t)t * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = sum_splits(a, a_splits, split_stride, base + i);
+    if (bias != nullptr) v += to_f32(bias[i]);
+    row[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = x[base + i] + row[i] * inv * to_f32(w[i]);
+    x[base + i] = v;
+    if (copy != nullptr) copy[base + i] = from_f32<T>(v);
+  }
+}
+
+// ---- the stream rounded to T ------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads) stream_round_kernel(T* __restrict__ out, const float* __restrict__ x,
+                                                                long long n) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += (long long)gridDim.x * kThreads)
+    out[i] = from_f32<T>(x[i]);
+}
+
+// ---- out = ca * a + cb * b over 32-bit products (or split-K partial products) -------------------
+__global__ void __launch_bounds__(kThreads) weighted_sum_kernel(float* __restrict__ out, const float* __restrict__ a,
+                                                                int a_splits, const float* __restrict__ b, int b_splits,
+                                                                long long n, float ca, float cb) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += (long long)gridDim.x * kThreads)
+    out[i] = ca * sum_splits(a, a_splits, n, (size_t)i) + cb * sum_splits(b, b_splits, n, (size_t)i);
+}
+
 // ---- [x; x0] rounded to T -------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(kThreads) concat_kernel(T* __restrict__ out, const float* __restrict__ x,
@@ -280,6 +354,57 @@ LAB_EXPORT int lab_stream_add_norm(float* out_a, void* out_b, float* x, const fl
     lab_launch(stream_add_norm_kernel<__nv_bfloat16>, dim3(n_out), dim3(threads), 0, stream, out_a,
                (__nv_bfloat16*)out_b, x, a, a_splits, b, b_splits, (const __nv_bfloat16*)sa, (const __nv_bfloat16*)sb,
                stride, mult, (const __nv_bfloat16*)wa, (const __nv_bfloat16*)wb, rows, n_in, hidden, eps, offset);
+  LAB_LAUNCH_CHECK();
+}
+
+LAB_EXPORT int lab_embed_position(float* out, const void* table, const void* pos_table, const int* ids,
+                                  const int* positions, int tokens, int hidden, int vocab, int max_positions, int dtype,
+                                  cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (dtype == LAB_F32)
+    lab_launch(embed_position_kernel<float>, dim3(tokens), dim3(kThreads), 0, stream, out,
+               (const float*)table, (const float*)pos_table, ids, positions, hidden, vocab, max_positions);
+  else
+    lab_launch(embed_position_kernel<__nv_bfloat16>, dim3(tokens), dim3(kThreads), 0, stream, out,
+               (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, ids, positions, hidden, vocab,
+               max_positions);
+  LAB_LAUNCH_CHECK();
+}
+
+LAB_EXPORT int lab_stream_norm_add(float* x, void* copy, const float* a, int a_splits, const void* bias, const void* w,
+                                   int tokens, int hidden, float eps, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const long long stride = (long long)tokens * hidden;
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (smem > 160 * 1024) return (int)cudaErrorInvalidValue;
+  const int threads = tokens <= 64 ? (hidden >= 1024 ? 1024 : (hidden + 31) / 32 * 32) : kThreads;
+  if (dtype == LAB_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(stream_norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    lab_launch(stream_norm_add_kernel<float>, dim3(tokens), dim3(threads), smem, stream, x, (float*)copy, a, a_splits,
+               stride, (const float*)bias, (const float*)w, hidden, eps);
+  } else {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(stream_norm_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    lab_launch(stream_norm_add_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), smem, stream, x, (__nv_bfloat16*)copy,
+               a, a_splits, stride, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)w, hidden, eps);
+  }
+  LAB_LAUNCH_CHECK();
+}
+
+LAB_EXPORT int lab_stream_round(void* out, const float* x, long long n, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (dtype == LAB_F32)
+    lab_launch(stream_round_kernel<float>, dim3(blocks_for(n)), dim3(kThreads), 0, stream, (float*)out, x, n);
+  else
+    lab_launch(stream_round_kernel<__nv_bfloat16>, dim3(blocks_for(n)), dim3(kThreads), 0, stream, (__nv_bfloat16*)out, x, n);
+  LAB_LAUNCH_CHECK();
+}
+
+LAB_EXPORT int lab_weighted_sum(float* out, const float* a, int a_splits, const float* b, int b_splits, long long n,
+                                float ca, float cb, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  lab_launch(weighted_sum_kernel, dim3(blocks_for(n)), dim3(kThreads), 0, stream, out, a, a_splits, b, b_splits, n, ca, cb);
   LAB_LAUNCH_CHECK();
 }
 

@@ -28,7 +28,7 @@ from ..cache import manager as cache_mod
 from ..kernels import ops
 from ..models.builder import CausalLM, load_model
 from ..parts.base import CacheView, GroupView, StepContext
-from ..parts.spec import FixedState, PagedKV, PagedLatent
+from ..parts.spec import CacheParts, FixedState, PagedKV, PagedLatent
 from .. import profiling
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32,
@@ -98,29 +98,16 @@ class Engine:
         self.cache = rt.CacheManager(groups, self.max_requests)
         self.group_windows = list(plan.group_windows)
         self.views: list[CacheView] = []
-        for need, block_need, group in zip(plan.needs, plan.block_needs, plan.group_of):
+        for need, block_need in zip(plan.needs, plan.block_needs):
             block_state = None
             if isinstance(block_need, FixedState):
                 block_state = torch.zeros((self.max_requests,) + tuple(block_need.shape), dtype=torch.float32,
                                           device=self.device)
             elif block_need is not None:
                 raise ValueError("a block arrangement may keep fixed-size state only")
-            if isinstance(need, PagedLatent):
-                latent = torch.empty((self.num_pages, self.page_size, need.width), dtype=self.dtype, device=self.device)
-                self.views.append(CacheView(need, group=group, k=latent, block_state=block_state))
-            elif isinstance(need, PagedKV):
-                shape = (self.num_pages, need.n_kv_heads, self.page_size, need.head_dim)
-                # Pages are never cleared: what may be read is decided by lengths alone.
-                k = torch.empty(shape, dtype=self.dtype, device=self.device)
-                v = torch.empty(shape, dtype=self.dtype, device=self.device)
-                self.views.append(CacheView(need, group=group, k=k, v=v, block_state=block_state))
-            elif isinstance(need, FixedState):
-                state = torch.zeros((self.max_requests,) + tuple(need.shape), dtype=torch.float32, device=self.device)
-                self.views.append(CacheView(need, state=state, block_state=block_state))
-            else:
-                self.views.append(CacheView(None, block_state=block_state))
+            self.views.append(self._new_view(need, plan, block_state))
         # every tensor of fixed-size per-request state, the mixers' and the blocks' own
-        self.state_tensors = [t for v in self.views for t in (v.state, v.block_state) if t is not None]
+        self.state_tensors = [t for v in self.views for t in self._states_of(v)]
         self.stateful = bool(self.state_tensors)
         # Decode steps of a stateful model may run from CUDA graphs if every block and mixer says so
         # (`Part.decode_graph_safe`); models without fixed-size state always may.
@@ -140,6 +127,33 @@ class Engine:
         self.graph_replays = 0
 
     # ------------------------------------------------------------------------------------
+    def _new_view(self, need, plan, block_state=None) -> CacheView:
+        """The storage one need asks for: pages of keys and values, pages of latents, fixed-size state per
+        request slot, or, for a need made of parts, a view per part."""
+        if isinstance(need, CacheParts):
+            return CacheView(need, parts=[self._new_view(part, plan) for part in need.parts], block_state=block_state)
+        if isinstance(need, PagedLatent):
+            latent = torch.empty((self.num_pages, self.page_size, need.width), dtype=self.dtype, device=self.device)
+            return CacheView(need, group=plan.group_for(need), k=latent, block_state=block_state)
+        if isinstance(need, PagedKV):
+            shape = (self.num_pages, need.n_kv_heads, self.page_size, need.head_dim)
+            # Pages are never cleared: what may be read is decided by lengths alone.
+            k = torch.empty(shape, dtype=self.dtype, device=self.device)
+            v = torch.empty(shape, dtype=self.dtype, device=self.device)
+            return CacheView(need, group=plan.group_for(need), k=k, v=v, block_state=block_state)
+        if isinstance(need, FixedState):
+            state = torch.zeros((self.max_requests,) + tuple(need.shape), dtype=torch.float32, device=self.device)
+            return CacheView(need, state=state, block_state=block_state)
+        return CacheView(None, block_state=block_state)
+
+    @classmethod
+    def _states_of(cls, view: CacheView):
+        for t in (view.state, view.block_state):
+            if t is not None:
+                yield t
+        for part in view.parts or ():
+            yield from cls._states_of(part)
+
     def _new_staging(self):
         n_groups = len(self.group_windows)
         cap_t, cap_b = self.max_batch_tokens, self.max_requests

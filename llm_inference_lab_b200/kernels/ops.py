@@ -606,10 +606,15 @@ def _tc_operands(x, w) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def linear(x, w, bias=None, out_f32=False, allow_partial=False, out=None):
+def linear(x, w, bias=None, out_f32=False, allow_partial=False, out=None, act=None):
     """x @ w.T (+ bias).  With `allow_partial` the result may come back as 32-bit partial
     products [splits, tokens, out], without the bias, that the consumer sums (`add_rmsnorm`,
-    `rope_kv_write`, `stream_add`).  `out`: where the result goes (rows may be strided)."""
+    `rope_kv_write`, `stream_add`).  `out`: where the result goes (rows may be strided).  `act`:
+    an activation of the result ("gelu_tanh"), applied after the bias and before the rounding."""
+    if act is not None:
+        if act != "gelu_tanh" or allow_partial:
+            raise KernelError(f"linear: activation {act!r} is not built, or asked of partial products")
+        return gelu_tanh_(linear(x, w, bias, out_f32=out_f32, out=out))
     if x.dtype == torch.float32 or _force_plain or not _tc_operands(x, w) or (
             out is not None and (out.stride(0) % 8 or out.data_ptr() % 16)):
         return gemm_plain(x, w, bias, out_f32=out_f32, out=out)
@@ -691,7 +696,7 @@ def decode_splits(n_decode: int, n_kv: int, group: int, max_kv_len: int, keys_pe
 def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requests, q_lens, max_kv_len,
                  n_q, n_kv, head_dim, window, scale, out=None, splits=None, scratch=None):
     """Tensor-core attention: the prefill kernel serves requests with several new tokens,
-    the split-KV decode kernel those with one."""
+    the split-KV decode kernel those with one.  A negative `window` means chunks of that many positions."""
     _on_gpu(q, cache_k, cache_v, q_start, kv_len, pos0, block_table)
     if q.dtype != torch.bfloat16 or not attention_tc_supported(head_dim):
         raise KernelError(f"attention_tc: bfloat16 and a head size multiple of 16 up to 128, got {q.dtype}, {head_dim}")
@@ -720,7 +725,7 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
                                        window, ctypes.c_float(scale), 2, None, _stream()), "attention_prefill")
     if n_decode:
         if splits is None:
-            span = min(max_kv_len, window) if window else max_kv_len
+            span = min(max_kv_len, abs(window)) if window else max_kv_len     # a chunk reaches as far as a window
             splits = decode_splits(n_decode, n_kv, n_q // n_kv, span, *decode_shape(head_dim))
         ctas = n_decode * n_kv * (-(-(n_q // n_kv) // 16)) * splits
         in_cluster = CLUSTER_MERGE and 2 <= splits <= 8 and ctas <= sm_count()
@@ -738,7 +743,14 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
     return out
 
 
-def attention(q, cache_k, cache_v, ctx, group, n_q, n_kv, head_dim, window, scale):
+def attention(q, cache_k, cache_v, ctx, group, n_q, n_kv, head_dim, window, scale, chunk=0):
+    """Causal attention of every row over its request's cached keys: all of them, the last `window`, or
+    (with `chunk`) those of the row's own chunk of `chunk` positions, chunks counted from position 0.  The
+    kernels take the mask as one number: a window as it is, a chunk as its negative."""
+    if chunk:
+        if window:
+            raise KernelError("attention takes a window or a chunk, not both")
+        window = -int(chunk)
     if q.dtype == torch.bfloat16 and not _force_plain and attention_tc_supported(head_dim):
         return attention_tc(q, cache_k, cache_v, ctx.q_start, ctx.kv_len, ctx.pos0, group.block_table,
                             ctx.n_requests, ctx.q_lens, ctx.max_kv_len, n_q, n_kv, head_dim, window, scale)
@@ -1060,3 +1072,219 @@ def latent_attention_plain_form(q: torch.Tensor, cache: torch.Tensor, w_up: torc
                                     ctx.n_requests, ctx.max_q_len, heads, heads, page_size, num_pages, window,
                                     ctypes.c_float(scale), int(at_least), _ptr(sink), _stream()), "attention_prefill")
     return out
+
+
+# ----------------------------------------------------------------------------------------
+# A 32-bit stream with learned positions and normed sublayer outputs (csrc/kernels/stream32.cu).
+# ----------------------------------------------------------------------------------------
+def embed_position(ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, pos_table: torch.Tensor) -> torch.Tensor:
+    """32-bit rows table[id] + pos_table[position]."""
+    _on_gpu(ids, positions, table, pos_table)
+    tokens, (vocab, hidden) = ids.numel(), table.shape
+    assert ids.dtype == torch.int32 and positions.dtype == torch.int32 and positions.numel() == tokens
+    assert table.is_contiguous() and pos_table.is_contiguous() and pos_table.shape[1] == hidden
+    assert pos_table.dtype == table.dtype
+    out = torch.empty((tokens, hidden), dtype=torch.float32, device=table.device)
+    _check(lib("stream32").lab_embed_position(_ptr(out), _ptr(table), _ptr(pos_table), _ptr(ids),
+                                              _ptr(positions), tokens, hidden, vocab, pos_table.shape[0],
+                                              dtype_code(table.dtype), _stream()), "embed_position")
+    return out
+
+
+def stream_norm_add(x: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, eps: float,
+                    bias: torch.Tensor | None = None, copy: bool = False) -> torch.Tensor | None:
+    """x += rmsnorm(a + bias) * weight in place on the 32-bit stream; `a` is a 32-bit product [tokens, hidden]
+    or split-K partial products [splits, tokens, hidden] (summed in ascending order).  With `copy`, returns
+    the new rows of x rounded to the weight's storage type."""
+    _on_gpu(x, a, weight, bias)
+    tokens, hidden = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and a.dtype == torch.float32 and a.is_contiguous()
+    assert a.shape[-2:] == x.shape and weight.numel() == hidden and (bias is None or bias.dtype == weight.dtype)
+    splits = a.shape[0] if a.dim() == 3 else 1
+    rounded = torch.empty((tokens, hidden), dtype=weight.dtype, device=x.device) if copy else None
+    _check(lib("stream32").lab_stream_norm_add(_ptr(x), _ptr(rounded), _ptr(a), splits, _ptr(bias), _ptr(weight), tokens,
+                                               hidden, ctypes.c_float(eps), dtype_code(weight.dtype), _stream()),
+           "stream_norm_add")
+    return rounded
+
+
+def stream_round(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The 32-bit stream rounded to `dtype` (the stream itself where that is 32-bit)."""
+    if dtype == torch.float32:
+        return x
+    _on_gpu(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _check(lib("stream32").lab_stream_round(_ptr(out), _ptr(x), ctypes.c_longlong(x.numel()), dtype_code(dtype), _stream()),
+           "stream_round")
+    return out
+
+
+def weighted_sum(a: torch.Tensor, ca: float, b: torch.Tensor, cb: float) -> torch.Tensor:
+    """ca * a + cb * b over 32-bit products [tokens, hidden] or split-K partial products [splits, tokens, hidden]."""
+    _on_gpu(a, b)
+    assert a.dtype == torch.float32 and b.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous()
+    assert a.shape[-2:] == b.shape[-2:]
+    out = torch.empty(a.shape[-2:], dtype=torch.float32, device=a.device)
+    _check(lib("stream32").lab_weighted_sum(_ptr(out), _ptr(a), a.shape[0] if a.dim() == 3 else 1, _ptr(b),
+                                            b.shape[0] if b.dim() == 3 else 1, ctypes.c_longlong(out.numel()),
+                                            ctypes.c_float(ca), ctypes.c_float(cb), _stream()), "weighted_sum")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# Attention with norms over the whole q and k projections and a gate (csrc/kernels/norm_attention.cu).
+# ----------------------------------------------------------------------------------------
+def padded_head(dim: int, vdim: int) -> int:
+    """The width heads of `dim` keys and `vdim` values are stored at: the larger one rounded up to a multiple
+    of 16 (the tensor-core attention's step)."""
+    return (max(dim, vdim) + 15) // 16 * 16
+
+
+def qk_norm_store(proj: torch.Tensor, bias, w_q: torch.Tensor, w_k, slots, cache_k, cache_v, n_q: int, n_kv: int,
+                  dim: int, vdim: int, head: int, eps: float, has_kv: bool = True) -> torch.Tensor:
+    """From the 32-bit fused projection `proj` [tokens, >= q + k + v columns] (or split-K partial products
+    [splits, tokens, ...]) and an optional bias over those columns: q and k RMS-normed over their whole
+    projections with the weights `w_q`, `w_k`; q returned [tokens, n_q * head] in the weights' storage type,
+    heads padded with zeros to `head` entries; k and v written the same way into their cache slots
+    (`cache_k` None: nothing is written).  `has_kv` False: the projection holds q only."""
+    _on_gpu(proj, bias, w_q, w_k, slots, cache_k, cache_v)
+    splits = proj.shape[0] if proj.dim() == 3 else 1
+    tokens, ld = proj.shape[-2], proj.shape[-1]
+    assert proj.dtype == torch.float32 and proj.is_contiguous()
+    need = n_q * dim + (n_kv * (dim + vdim) if has_kv else 0)
+    assert ld >= need and w_q.numel() == n_q * dim and (not has_kv or w_k.numel() == n_kv * dim)
+    assert bias is None or (bias.numel() >= need and bias.dtype == w_q.dtype)
+    dt = w_q.dtype
+    page_size = num_pages = 0
+    if cache_k is not None:
+        num_pages, kvh, page_size, d = cache_k.shape
+        assert has_kv and kvh == n_kv and d == head and cache_k.is_contiguous() and cache_v.is_contiguous()
+        assert cache_v.shape == cache_k.shape and cache_k.dtype == dt and slots is not None and slots.dtype == torch.int32
+    q = torch.empty((tokens, n_q * head), dtype=dt, device=proj.device)
+    _check(lib("norm_attention").lab_qk_norm_store(
+        _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v), _ptr(proj), splits, ld, _ptr(bias), _ptr(w_q), _ptr(w_k),
+        _ptr(slots), tokens, n_q, n_kv, dim, vdim, head, page_size, num_pages, int(has_kv), ctypes.c_float(eps),
+        dtype_code(dt), _stream()), "qk_norm_store")
+    return q
+
+
+def head_gate(attn: torch.Tensor, proj: torch.Tensor, gate_at: int, per_head: bool, n_q: int, vdim: int, head: int,
+              mult: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t, h * vdim + i] = attn[t, h * head + i] * sigmoid(g) * mult with g = proj[t, gate_at + h] (`per_head`)
+    or proj[t, gate_at + h * vdim + i]; `proj` 32-bit, whole or split-K partial products.  `out` may be a
+    column slice of a wider buffer."""
+    _on_gpu(attn, proj, out)
+    splits = proj.shape[0] if proj.dim() == 3 else 1
+    tokens, ld = proj.shape[-2], proj.shape[-1]
+    assert proj.dtype == torch.float32 and proj.is_contiguous() and attn.stride(1) == 1 and attn.shape[0] == tokens
+    assert ld >= gate_at + (n_q if per_head else n_q * vdim)
+    if out is None:
+        out = torch.empty((tokens, n_q * vdim), dtype=attn.dtype, device=attn.device)
+    assert out.dtype == attn.dtype and out.stride(1) == 1 and out.shape == (tokens, n_q * vdim)
+    _check(lib("norm_attention").lab_head_gate(_ptr(out), out.stride(0), _ptr(attn), attn.stride(0), _ptr(proj), splits, ld,
+                                               gate_at, int(per_head), tokens, n_q, vdim, head, ctypes.c_float(mult),
+                                               dtype_code(attn.dtype), _stream()), "head_gate")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# Recurrent mixers with a scalar decay (csrc/kernels/linear_state.cu).
+# ----------------------------------------------------------------------------------------
+def decay_scan_supported(keys: int) -> bool:
+    return 1 <= keys <= 256
+
+
+def decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, ctx, heads: int, groups: int,
+               keys: int, vdim: int, a_head: torch.Tensor | None = None, a_tok: torch.Tensor | None = None,
+               s_tok: torch.Tensor | None = None, silu: bool = False, write: bool = True) -> torch.Tensor:
+    """Per request and head, over the step's rows in order: S <- a S + (s k) v^T, o = S^T q, with S
+    [keys, vdim] read from and (with `write`) left in `state` [slots, heads, keys, vdim].  q and k are 32-bit
+    column slices [tokens, groups * keys] of one tensor (same row stride), v [tokens, heads * vdim]; `a_head`
+    [heads] a fixed decay per head, or `a_tok`/`s_tok` [tokens, heads] per token; `silu`: q, k and v pass a
+    SiLU first.  Returns o [tokens, heads * vdim] in 32-bit."""
+    _on_gpu(q, k, v, state, a_head, a_tok, s_tok)
+    tokens = v.shape[0]
+    for t in (q, k, v):
+        assert t.dtype == torch.float32 and t.stride(1) == 1 and t.shape[0] == tokens
+    assert q.stride(0) == k.stride(0) and q.shape[1] == groups * keys and v.shape[1] == heads * vdim
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, keys, vdim)
+    assert (a_head is None) != (a_tok is None)
+    ld_a = 0
+    if a_tok is not None:
+        assert a_tok.dtype == torch.float32 and a_tok.shape == (tokens, heads) and a_tok.stride(1) == 1
+        assert s_tok is None or (s_tok.dtype == torch.float32 and s_tok.shape == (tokens, heads)
+                                 and s_tok.stride(0) == a_tok.stride(0))
+        ld_a = a_tok.stride(0)
+    else:
+        assert a_head.dtype == torch.float32 and a_head.numel() == heads and s_tok is None
+    if not decay_scan_supported(keys):
+        raise KernelError(f"decay_scan: {keys} key channels are outside what the recurrence kernel takes (1..256)")
+    out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=v.device)
+    # columns of the state per CTA: narrow slices when a step has few (request, head) pairs, so that more SMs work
+    pairs = ctx.n_requests * heads
+    vs = 32 if pairs * -(-vdim // 32) >= sm_count() else (16 if pairs * -(-vdim // 16) >= sm_count() else 8)
+    vs = min(vs, max(8, 1 << (vdim - 1).bit_length()))
+    _check(lib("linear_state").lab_decay_scan(
+        _ptr(out), out.stride(0), _ptr(q), _ptr(k), q.stride(0), _ptr(v), v.stride(0), _ptr(a_tok), _ptr(s_tok), ld_a,
+        _ptr(a_head), _ptr(state), _ptr(ctx.q_start), _ptr(ctx.state_slot), ctx.n_requests, state.shape[0], heads, groups,
+        keys, vdim, int(silu), int(write), vs, _stream()), "decay_scan")
+    return out
+
+
+def ssm_prepare(proj: torch.Tensor, conv_at: int, dt_at: int, channels: int, taps: int, heads: int,
+                taps_w: torch.Tensor, taps_b: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+                kept: torch.Tensor, ctx, write: bool = True):
+    """From the 32-bit input projection `proj` of a state-space mixer: columns [conv_at, conv_at + channels)
+    pass the causal convolution per channel (`taps_w` [channels, taps], last tap on the row itself; the
+    inputs before a request's first row of the step come from `kept` [slots, taps - 1, channels], which with
+    `write` then takes the request's last inputs) with bias and SiLU; columns [dt_at, dt_at + heads) give
+    dt = softplus(. + dt_bias) and the decay exp(-exp(a_log) * dt).  Returns (convolved, dt, decay), 32-bit."""
+    _on_gpu(proj, taps_w, taps_b, dt_bias, a_log, kept)
+    tokens, ld = proj.shape
+    assert proj.dtype == torch.float32 and proj.is_contiguous() and ld >= max(conv_at + channels, dt_at + heads)
+    assert taps_w.shape == (channels, taps) and taps_w.is_contiguous() and taps_b.numel() == channels
+    assert dt_bias.numel() == heads and a_log.numel() == heads
+    assert all(t.dtype == taps_w.dtype for t in (taps_b, dt_bias, a_log))
+    assert kept.dtype == torch.float32 and kept.is_contiguous() and kept.shape[1:] == (max(taps - 1, 0), channels)
+    conv = torch.empty((tokens, channels), dtype=torch.float32, device=proj.device)
+    dt = torch.empty((tokens, heads), dtype=torch.float32, device=proj.device)
+    decay = torch.empty((tokens, heads), dtype=torch.float32, device=proj.device)
+    _check(lib("linear_state").lab_ssm_prepare(
+        _ptr(conv), _ptr(dt), _ptr(decay), _ptr(proj), ld, conv_at, dt_at, channels, taps, heads, _ptr(taps_w),
+        _ptr(taps_b), _ptr(dt_bias), _ptr(a_log), _ptr(kept), _ptr(ctx.row_req), _ptr(ctx.q_start), _ptr(ctx.state_slot),
+        tokens, ctx.n_requests, kept.shape[0], int(write), dtype_code(taps_w.dtype), _stream()), "ssm_prepare",
+        2 if write and taps > 1 else 1)
+    return conv, dt, decay
+
+
+def gated_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, parts: int = 1,
+               gate_first: bool = False, skip: torch.Tensor | None = None, x: torch.Tensor | None = None,
+               head_size: int = 1, mult: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The heads' outputs `o` [tokens, width] (32-bit; + skip[head] * x), gated and RMS-normed in `parts` equal
+    parts with `weight`: `gate_first`, y * silu(gate) then the norm; else the norm then * sigmoid(gate).  `gate`
+    and `x` are 32-bit column slices.  The result, times `mult`, is rounded to the weight's storage type."""
+    _on_gpu(o, gate, weight, skip, x, out)
+    tokens, width = o.shape
+    assert o.dtype == torch.float32 and o.stride(1) == 1 and gate.dtype == torch.float32 and gate.stride(1) == 1
+    assert gate.shape == o.shape and weight.numel() == width and width % parts == 0
+    assert (skip is None) == (x is None)
+    if skip is not None:
+        assert x.dtype == torch.float32 and x.stride(1) == 1 and x.shape == o.shape and skip.dtype == weight.dtype
+        assert skip.numel() * head_size == width
+    if out is None:
+        out = torch.empty((tokens, width), dtype=weight.dtype, device=o.device)
+    assert out.dtype == weight.dtype and out.stride(1) == 1 and out.shape == (tokens, width)
+    _check(lib("linear_state").lab_gated_norm(
+        _ptr(out), out.stride(0), _ptr(o), o.stride(0), _ptr(x), x.stride(0) if x is not None else 0, _ptr(skip),
+        head_size, _ptr(gate), gate.stride(0), _ptr(weight), tokens, width, parts, int(gate_first), ctypes.c_float(eps),
+        ctypes.c_float(mult), dtype_code(weight.dtype), _stream()), "gated_norm")
+    return out
+
+
+def gelu_tanh_(x: torch.Tensor) -> torch.Tensor:
+    """x <- 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) in place (32-bit arithmetic, one rounding)."""
+    _on_gpu(x)
+    assert x.is_contiguous()
+    _check(lib("rowwise").lab_gelu_tanh(_ptr(x), ctypes.c_longlong(x.numel()), dtype_code(x.dtype), _stream()), "gelu_tanh")
+    return x

@@ -16,7 +16,7 @@ import torch
 
 from ..parts.base import CacheView, StepContext, lookup
 from ..profiling import scoped_range
-from ..parts.spec import CacheNeed, ModelBlueprint, PagedKV, PagedLatent, TensorSpec
+from ..parts.spec import CacheNeed, CacheParts, ModelBlueprint, PagedKV, PagedLatent, TensorSpec
 
 
 # False: pure decode steps run part by part as every other step does (tests compare the two).
@@ -68,6 +68,22 @@ class CachePlan:
     block_needs: tuple[CacheNeed, ...]      # by cache id: fixed-size state of the block arrangement itself
     group_of: tuple[int, ...]               # cache id -> group index (-1: no paged group)
     group_windows: tuple[int, ...]          # per paged group: 0 or the window
+    group_keys: tuple = ()                  # per paged group: the key its needs share
+
+    def group_for(self, need: CacheNeed) -> int:
+        """The paged group of a need (also of one part of a need made of parts); -1 if it is not paged."""
+        if isinstance(need, (PagedKV, PagedLatent)):
+            return self.group_keys.index(need.group_key())
+        return -1
+
+
+def _paged_needs(need: CacheNeed):
+    """The paged needs inside a need, parts included."""
+    if isinstance(need, CacheParts):
+        for part in need.parts:
+            yield from _paged_needs(part)
+    elif isinstance(need, (PagedKV, PagedLatent)):
+        yield need
 
 
 def cache_plan(bp: ModelBlueprint) -> CachePlan:
@@ -93,14 +109,11 @@ def cache_plan(bp: ModelBlueprint) -> CachePlan:
     keys: list = []
     group_of = []
     for need in needs:
-        if isinstance(need, (PagedKV, PagedLatent)):
-            key = need.group_key()
-            if key not in keys:
-                keys.append(key)
-            group_of.append(keys.index(key))
-        else:
-            group_of.append(-1)
-    return CachePlan(tuple(needs), tuple(block_needs), tuple(group_of), tuple(k[1] for k in keys))
+        for paged in _paged_needs(need):
+            if paged.group_key() not in keys:
+                keys.append(paged.group_key())
+        group_of.append(keys.index(need.group_key()) if isinstance(need, (PagedKV, PagedLatent)) else -1)
+    return CachePlan(tuple(needs), tuple(block_needs), tuple(group_of), tuple(k[1] for k in keys), tuple(keys))
 
 
 class CausalLM:
@@ -137,7 +150,7 @@ class CausalLM:
         `pick` = (temperatures, seeds, positions, out), each [len(logit_rows)] on the device, it returns one
         token per wanted row instead (`Head.pick`)."""
         with scoped_range("embedding"):
-            x = self.embedding.forward(ctx.token_ids)
+            x = self.embedding.forward(ctx.token_ids, ctx.row_pos)
         pending = None
         stack = self.decode_stack
         if stack is not None and USE_DECODE_STACK and stack.serves(ctx, caches):

@@ -12,7 +12,7 @@ registry           interface
 ``NORMS``          `Norm`: ``forward(x, rows=None)``, ``forward_add(x, delta, rows=None)``
 ``POSITIONS``      `PositionEncoding`: ``rotate_and_store(...)``
 ``BLOCKS``         `Block`: ``forward(x, pending, ctx, cache)``
-``EMBEDDINGS``     `Embedding`: ``forward(token_ids)``
+``EMBEDDINGS``     `Embedding`: ``forward(token_ids, positions)``
 ``HEADS``          `Head`: ``forward(x)`` giving 32-bit logits
 ``REENTRIES``      `StreamReentry`: ``forward(x, x0)`` between two layer calls
 =================  ==========================================================
@@ -74,6 +74,12 @@ class CacheView:
     v: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None    # [max_requests, *shape] float32
     block_state: Optional[torch.Tensor] = None   # fixed-size state of the block arrangement itself, same form
+    parts: Optional[list] = None            # a need made of parts (`CacheParts`): one view per part
+
+    def part(self, index: int) -> "CacheView":
+        """The view of part `index` of a need made of parts; it writes only if this view does."""
+        view = self.parts[index]
+        return view if view.write == self.write else dataclasses.replace(view, write=self.write)
 
 
 class Part:
@@ -191,7 +197,9 @@ class StreamReentry(Part):
 
 
 class Embedding(Part):
-    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+    def forward(self, token_ids: torch.Tensor, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Rows of the residual stream for `token_ids`; `positions` [tokens] int32 are the rows' positions
+        in their sequences, for embeddings that encode them."""
         raise NotImplementedError
 
 

@@ -139,3 +139,61 @@ class ParallelStreamBlock(Block):
 
 
 register_part("block", "parallel_stream", ParallelStreamBlock)
+
+
+@dataclasses.dataclass
+class RoundedStream:
+    """What a block that owes the stream nothing hands on: the rows of the stream as it left them, already
+    rounded to the storage type, for a next block whose sublayers read the stream itself."""
+    rows: torch.Tensor
+
+    def add_to(self, x):      # nothing is owed
+        return x
+
+
+class NormedSublayersBlock(Block):
+    """Each sublayer reads the 32-bit residual stream itself and its *output* is normed before the sum:
+
+        x <- x + norm1(mixer(x));   x <- x + norm2(ffn(x))
+
+    (RMS norms with plain weights; a layer may have no feed-forward.)  The sublayers' products arrive in
+    32-bit, whole or as split-K partial products; one kernel sums them, norms, adds to the stream and leaves
+    the new rows rounded for the product that reads them next, so the block hands the next one those rows
+    as `pending` (`RoundedStream`) and owes the stream nothing."""
+    decode_graph_safe = True
+
+    n_norms = 2
+
+    @classmethod
+    def libraries(cls, spec, dtype):
+        return [("stream32", {})]
+
+    def __init__(self, mixer, ffn, norms, spec=None, weights=None, dtype=None, device=None):
+        super().__init__(mixer, ffn, norms, spec, weights, dtype, device)
+        self.dtype = dtype
+        for n in norms[: 2 if ffn is not None else 1]:
+            if type(n) is not StreamRMSNorm or n.offset != 0.0:
+                raise ValueError("normed_sublayers_stream: the norms are rmsnorm_stream with plain weights")
+
+    def forward(self, x, pending, ctx, cache):
+        if isinstance(pending, RoundedStream):
+            h = pending.rows
+        else:
+            if pending is not None:
+                if not hasattr(pending, "add_to"):
+                    raise ValueError("normed_sublayers_stream follows a block whose sum it cannot take")
+                pending.add_to(x)
+            h = ops.stream_round(x, self.dtype)
+        n1 = self.norms[0]
+        with scoped_range(self.mixer_range):
+            a = self.mixer.forward(h, ctx, cache)
+            h = ops.stream_norm_add(x, a, n1.weight, n1.eps, copy=self.dtype != torch.float32)
+        if self.ffn is not None:
+            n2 = self.norms[1]
+            with scoped_range(self.ffn_range):
+                f = self.ffn.forward(x if h is None else h, ctx)
+                h = ops.stream_norm_add(x, f, n2.weight, n2.eps, copy=self.dtype != torch.float32)
+        return x, RoundedStream(x if h is None else h)
+
+
+register_part("block", "normed_sublayers_stream", NormedSublayersBlock)

@@ -18,7 +18,7 @@ class TokenEmbedding(Embedding):
         self.table = self._weight(weights, "weight").contiguous()
         weights[spec.prefix + "weight"] = self.table   # a tied head shares this storage
 
-    def forward(self, token_ids):
+    def forward(self, token_ids, positions=None):
         return ops.embed(token_ids, self.table)
 
 
@@ -40,8 +40,35 @@ class NormedTokenEmbedding(Embedding):
         self.weight = w if w.dtype == dtype else w.to(dtype)
         self.eps, self.offset = float(spec["eps"]), float(spec.get("offset") or 0.0)
 
-    def forward(self, token_ids):
+    def forward(self, token_ids, positions=None):
         return ops.embed_norm(token_ids, self.table, self.weight, self.eps, self.offset)
+
+
+class TokenPositionEmbedding(Embedding):
+    """x[t] = table[id_t] + positions[p_t] as a 32-bit residual stream: a learned vector per absolute
+    position (the table's rows bound the longest sequence), added unscaled."""
+
+    @classmethod
+    def tensors(cls, spec: PartSpec):
+        return [TensorSpec(spec["table"], (spec["vocab"], spec["hidden"]), init="table"),
+                TensorSpec(spec["positions"], (spec["max_positions"], spec["hidden"]), init="table")]
+
+    @classmethod
+    def libraries(cls, spec, dtype):
+        return [("stream32", {})]
+
+    def __init__(self, spec, weights, dtype, device):
+        super().__init__(spec, weights, dtype, device)
+        t = weights[spec["table"]]
+        self.table = (t if t.dtype == dtype else t.to(dtype)).contiguous()
+        weights[spec["table"]] = self.table      # a tied head shares this storage
+        p = weights[spec["positions"]]
+        self.positions = (p if p.dtype == dtype else p.to(dtype)).contiguous()
+
+    def forward(self, token_ids, positions=None):
+        if positions is None:
+            raise ValueError("token_position_embedding needs the rows' positions")
+        return ops.embed_position(token_ids, positions, self.table, self.positions)
 
 
 class LinearHead(Head):
@@ -76,4 +103,5 @@ class LinearHead(Head):
 
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("embedding", "normed_token_embedding", NormedTokenEmbedding)
+register_part("embedding", "token_position_embedding", TokenPositionEmbedding)
 register_part("head", "linear_head", LinearHead)

@@ -45,3 +45,43 @@ class GatedMLP(FeedForward):
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)
+
+
+class DenseMLP(FeedForward):
+    """down( act(x Wu^T + bu) ) + bd: one matrix up, an activation, one matrix down, biases optional.  `act`
+    is "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).  The activation is the epilogue of
+    the up product where the product kernel has it."""
+
+    ACTS = ("gelu_tanh",)
+    NAMES = {"up": "up_proj.weight", "down": "down_proj.weight", "bias": ".bias"}
+
+    @classmethod
+    def names(cls, spec: PartSpec) -> dict:
+        return {**cls.NAMES, **(spec.get("names") or {})}
+
+    @classmethod
+    def tensors(cls, spec: PartSpec):
+        h, i, p, n = spec["hidden"], spec["intermediate"], spec.prefix, cls.names(spec)
+        out = [TensorSpec(p + n["up"], (i, h)), TensorSpec(p + n["down"], (h, i))]
+        if spec.get("bias"):
+            out += [TensorSpec(p + n["up"] + n["bias"], (i,), init="bias"),
+                    TensorSpec(p + n["down"] + n["bias"], (h,), init="bias")]
+        return out
+
+    def __init__(self, spec, weights, dtype, device):
+        super().__init__(spec, weights, dtype, device)
+        if spec["act"] not in self.ACTS:
+            raise ValueError(f"dense_mlp: activation {spec['act']!r} is not built (known: {self.ACTS})")
+        n = self.names(spec)
+        self.w_up = self._weight(weights, n["up"]).contiguous()
+        self.w_down = self._weight(weights, n["down"]).contiguous()
+        self.b_up = self._weight(weights, n["up"] + n["bias"]) if spec.get("bias") else None
+        self.b_down = self._weight(weights, n["down"] + n["bias"]) if spec.get("bias") else None
+        self.out_f32 = bool(spec.get("out_f32"))
+
+    def forward(self, x, ctx):
+        act = ops.linear(x, self.w_up, self.b_up, act="gelu_tanh")
+        return ops.linear(act, self.w_down, self.b_down, out_f32=self.out_f32)
+
+
+register_part("feed_forward", "dense_mlp", DenseMLP)

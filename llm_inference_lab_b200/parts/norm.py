@@ -46,7 +46,7 @@ class StreamRMSNorm(Norm):
         return ops.norm_stream(x, self.eps, self.offset, weight=self.weight, rows=rows)[1]
 
     def forward_add(self, x, delta, rows=None):
-        if delta is None:
+        if delta is None or not hasattr(delta, "a"):      # nothing owed (or rows already rounded: `RoundedStream`)
             return self.forward(x, rows)
         # what the block before still owes the stream (`parts.block.PendingSum`): added here, in the norm's pass
         return ops.stream_add_norm(x, delta.a, delta.scale_a, delta.b, delta.scale_b, delta.mult, self.eps, self.offset,

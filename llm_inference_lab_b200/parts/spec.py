@@ -124,4 +124,15 @@ class FixedState:
         return ("fixed_state",)
 
 
-CacheNeed = Optional[PagedKV | PagedLatent | FixedState]
+@dataclasses.dataclass(frozen=True)
+class CacheParts:
+    """Several needs of one layer call, in a fixed order: a mixer made of mixers that each keep a cache
+    of their own, or one that keeps state of several shapes.  Each part is a need of the other kinds (or
+    None); the layer call's `CacheView.parts` holds one view per part."""
+    parts: tuple
+
+    def group_key(self):
+        return ("parts",)
+
+
+CacheNeed = Optional[PagedKV | PagedLatent | FixedState | CacheParts]

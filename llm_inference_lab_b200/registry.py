@@ -68,6 +68,8 @@ def _register_builtin() -> None:
     register_architecture("Qwen2ForCausalLM", Qwen2Config, qwen2_blueprint, model_types=("qwen2",))
     from .config.sogulix import SogulixConfig, sogulix_blueprint
     register_architecture("Sogulix", SogulixConfig, sogulix_blueprint)
+    from .config.ritizen import RitizenConfig, ritizen_blueprint
+    register_architecture("Ritizen", RitizenConfig, ritizen_blueprint)
 
 
 _register_builtin()
