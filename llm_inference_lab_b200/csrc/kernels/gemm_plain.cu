@@ -18,7 +18,7 @@ template <typename T, typename OutT, bool GATED>
 __global__ void __launch_bounds__(256) gemm_plain_kernel(OutT* __restrict__ out, const T* __restrict__ x,
                                                          const T* __restrict__ w, const T* __restrict__ bias, int M,
                                                          int N, int K, int ldx, int ldo, long long batch_x,
-                                                         long long batch_w, long long batch_o) {
+                                                         long long batch_w, long long batch_o, int gelu) {
   pdl_trigger();
   pdl_wait();
   // a batch of products of one shape (blockIdx.z): operand b lies b * batch_* elements further on
@@ -81,6 +81,7 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(OutT* __restrict__ out,
         v = g / (1.f + expf(-g)) * u;
       } else {
         v = acc[0][i][j] + (bias ? to_f32<T>(bias[n]) : 0.f);
+        if (gelu) v = gelu_tanh_f(v);      // the tanh form of GELU after the bias, before the rounding
       }
       out[(size_t)m * ldo + n] = from_f32<OutT>(v);
     }
@@ -134,15 +135,16 @@ template <typename T, typename OutT>
 int launch(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx, int ldo, int gated,
            cudaStream_t stream, int batch = 1, long long batch_x = 0, long long batch_w = 0, long long batch_o = 0) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
-  if (gated)
+  if (gated == 1)
     return (int)lab_launch(gemm_plain_kernel<T, OutT, true>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
-                           (const T*)w, (const T*)nullptr, M, N, K, ldx, ldo, batch_x, batch_w, batch_o);
+                           (const T*)w, (const T*)nullptr, M, N, K, ldx, ldo, batch_x, batch_w, batch_o, 0);
   return (int)lab_launch(gemm_plain_kernel<T, OutT, false>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
-                         (const T*)w, (const T*)bias, M, N, K, ldx, ldo, batch_x, batch_w, batch_o);
+                         (const T*)w, (const T*)bias, M, N, K, ldx, ldo, batch_x, batch_w, batch_o, gated == 2 ? 1 : 0);
 }
 }  // namespace
 
-// N is the number of output columns; with gated != 0, w holds 2 N rows (gate rows, then up rows).
+// N is the number of output columns; with gated == 1, w holds 2 N rows (gate rows, then up rows); gated == 2 is
+// the plain product with GELU (tanh form) after the bias.
 LAB_EXPORT int lab_gemm_plain(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx,
                               int ldo, int gated, int dtype, int out_f32, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;

@@ -99,6 +99,7 @@ struct Params {
   void* out;            // [tokens, ld_out] of OutT, or partial [splits, tokens, ld_out] floats;
                         // q/k/v: the rotated q [tokens, ld_out]
   const __nv_bfloat16* bias;
+  int gelu;             // plain epilogue: the tanh form of GELU after the bias, before the rounding
   int m_rows;           // valid rows on the M side (tokens, or features when swapped)
   int n_rows;           // valid rows on the N side
   int ld_out;
@@ -522,6 +523,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                   if (n + j < p.n_rows) v[j] += __bfloat162float(p.bias[n + j]);
               }
             }
+            if (p.gelu) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_f(v[j]);
+            }
             OutT* dst = (OutT*)p.out + (size_t)m * p.ld_out + n;
             if (n + 32 <= p.n_rows && (((uintptr_t)dst) & 15) == 0) {
               if (sizeof(OutT) == 2) {
@@ -600,7 +605,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             OutT* dst = (OutT*)p.out + m;
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-              if (t + j < p.n_rows) dst[(size_t)(t + j) * p.ld_out] = from_f32<OutT>(v[j] + b);
+              if (t + j < p.n_rows)
+                dst[(size_t)(t + j) * p.ld_out] = from_f32<OutT>(p.gelu ? gelu_tanh_f(v[j] + b) : v[j] + b);
           }
         }
         release();
@@ -756,10 +762,14 @@ __global__ void wait_probe_kernel(unsigned long long limit_ns, int* gave_up) {
 // out: bf16 or f32 [tokens, ld_out]; with splits > 1, `out` is the partial buffer
 // [splits, tokens, ld_out] of floats (no bias, not gated).
 // swap != 0: features on the M side (few tokens); bn: tile of the N side (16..256).
+// gated: 0 the plain product, 1 the SiLU-gated pair, 2 the plain product with GELU (tanh form) after the bias.
 LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* bias, int tokens, int n_out, int K,
                            int ldx, int ld_out, int gated, int out_f32, int swap, int bn, int splits,
                            cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
+  const int gelu = gated == 2;
+  if (gelu) gated = 0;
+  if (gelu && splits > 1) return (int)cudaErrorInvalidValue;
   if (K % 8 || ldx % 8 || K <= 0) return (int)cudaErrorInvalidValue;            // 16-byte rows for TMA
   if ((((uintptr_t)x) | ((uintptr_t)w)) & 15) return (int)cudaErrorInvalidValue;  // 16-byte bases for TMA
   if (splits < 1 || (splits > 1 && (gated || !out_f32))) return (int)cudaErrorInvalidValue;
@@ -767,6 +777,7 @@ LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* 
   Params p = {};
   p.out = out;
   p.bias = (const __nv_bfloat16*)bias;
+  p.gelu = gelu;
   p.ld_out = ld_out;
   p.split_stride = splits > 1 ? (long long)tokens * ld_out : 0;
   dim3 grid;

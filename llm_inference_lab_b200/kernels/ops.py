@@ -266,8 +266,10 @@ def rope_kv_write_table(qkv, table, rotary_dim, slots, cache_k, cache_v, n_q, n_
 
 
 def gemm_plain(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gated: bool = False,
-               out_f32: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
-    """out = x @ w.T (+ bias) on the ordinary arithmetic units; `gated`: silu(x@wg.T) * (x@wu.T), w = [wg; wu]."""
+               out_f32: bool = False, out: torch.Tensor | None = None, gelu: bool = False) -> torch.Tensor:
+    """out = x @ w.T (+ bias) on the ordinary arithmetic units; `gated`: silu(x@wg.T) * (x@wu.T), w = [wg; wu];
+    `gelu`: the tanh form of GELU after the bias, before the rounding."""
+    assert not (gated and gelu)
     _on_gpu(x, w, bias, out)
     M, K = x.shape
     N = w.shape[0] // 2 if gated else w.shape[0]
@@ -278,7 +280,8 @@ def gemm_plain(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = Non
         out = torch.empty((M, N), dtype=odt, device=x.device)
     assert out.dtype == odt and out.stride(1) == 1 and out.shape == (M, N)
     _check(lib("gemm_plain").lab_gemm_plain(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), M, N, K, x.stride(0),
-                                            out.stride(0), int(gated), dtype_code(x.dtype), int(out_f32), _stream()),
+                                            out.stride(0), 2 if gelu else int(gated), dtype_code(x.dtype), int(out_f32),
+                                            _stream()),
            "gemm_plain")
     return out
 
@@ -400,8 +403,9 @@ def force_plain(flag: bool) -> bool:
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gated: bool = False,
             out_f32: bool = False, swap: bool | None = None, bn: int | None = None, splits: int = 1,
-            out: torch.Tensor | None = None) -> torch.Tensor:
-    """out = x @ w.T (+ bias) on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulate).
+            out: torch.Tensor | None = None, gelu: bool = False) -> torch.Tensor:
+    """out = x @ w.T (+ bias) on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulate); `gelu`: the
+    tanh form of GELU after the bias, before the rounding (not with `gated` or `splits`).
 
     `swap` puts output features on the M side of the MMA (few tokens); `bn` is the tile on the
     other side; `splits` > 1 returns 32-bit partial products [splits, tokens, out].
@@ -439,13 +443,16 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, 
             out = torch.empty((T, n_out), dtype=odt, device=x.device)
         assert out.dtype == odt and out.stride(1) == 1
         ld_out, f32 = out.stride(0), out_f32
+    if gelu and (gated or splits > 1):
+        raise KernelError("gemm_tc: GELU goes with the plain, unsplit product")
     _check(lib("gemm_tc").lab_gemm_tc(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), T, n_out, K, x.stride(0), ld_out,
-                                      int(gated), int(f32), int(swap), bn, splits, _stream()), "gemm_tc")
+                                      2 if gelu else int(gated), int(f32), int(swap), bn, splits, _stream()), "gemm_tc")
     return out
 
 
 def gemm_tc2(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gated: bool = False,
-             out_f32: bool = False, splits: int = 1, out: torch.Tensor | None = None, bn: int = 0) -> torch.Tensor:
+             out_f32: bool = False, splits: int = 1, out: torch.Tensor | None = None, bn: int = 0,
+             gelu: bool = False) -> torch.Tensor:
     """out = x @ w.T (+ bias) on pairs of SMs (tcgen05.mma.cta_group::2): tiles of 256 tokens by 256
     accumulator columns, each CTA of a pair loading half of the weight tile.  For steps with many
     tokens; `splits` > 1 returns 32-bit partial products [splits, tokens, out].  `bn`: accumulator
@@ -472,8 +479,10 @@ def gemm_tc2(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
             out = torch.empty((T, n_out), dtype=odt, device=x.device)
         assert out.dtype == odt and out.stride(1) == 1
         ld_out, f32 = out.stride(0), out_f32
+    if gelu and (gated or splits > 1):
+        raise KernelError("gemm_tc2: GELU goes with the plain, unsplit product")
     _check(lib("gemm_tc2").lab_gemm_tc2(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), T, n_out, K, x.stride(0), ld_out,
-                                        int(gated), int(f32), splits, bn, _stream()), "gemm_tc2")
+                                        2 if gelu else int(gated), int(f32), splits, bn, _stream()), "gemm_tc2")
     return out
 
 
@@ -611,26 +620,25 @@ def linear(x, w, bias=None, out_f32=False, allow_partial=False, out=None, act=No
     products [splits, tokens, out], without the bias, that the consumer sums (`add_rmsnorm`,
     `rope_kv_write`, `stream_add`).  `out`: where the result goes (rows may be strided).  `act`:
     an activation of the result ("gelu_tanh"), applied after the bias and before the rounding."""
-    if act is not None:
-        if act != "gelu_tanh" or allow_partial:
-            raise KernelError(f"linear: activation {act!r} is not built, or asked of partial products")
-        return gelu_tanh_(linear(x, w, bias, out_f32=out_f32, out=out))
+    gelu = act is not None
+    if gelu and (act != "gelu_tanh" or allow_partial):
+        raise KernelError(f"linear: activation {act!r} is not built, or asked of partial products")
     if x.dtype == torch.float32 or _force_plain or not _tc_operands(x, w) or (
             out is not None and (out.stride(0) % 8 or out.data_ptr() % 16)):
-        return gemm_plain(x, w, bias, out_f32=out_f32, out=out)
+        return gemm_plain(x, w, bias, out_f32=out_f32, out=out, gelu=gelu)
     T = x.shape[0]
     if T > 128:
         kind, bn, splits = _pick_prefill_tiles(T, w.shape[0], x.shape[1],
                                                allow_partial and bias is None and out is None)
         if kind == "pair":
-            return gemm_tc2(x, w, bias, out_f32=out_f32, out=out)
+            return gemm_tc2(x, w, bias, out_f32=out_f32, out=out, gelu=gelu)
         if splits > 1:
             return gemm_tc(x, w, None, swap=False, bn=bn, splits=splits)
-        return gemm_tc(x, w, bias, out_f32=out_f32, swap=False, bn=bn, out=out)
+        return gemm_tc(x, w, bias, out_f32=out_f32, swap=False, bn=bn, out=out, gelu=gelu)
     splits = _pick_splits(T, w.shape[0], x.shape[1]) if allow_partial and out is None else 1
     if splits > 1:
         return gemm_tc(x, w, None, splits=splits)     # the consumer adds the bias
-    return gemm_tc(x, w, bias, out_f32=out_f32, out=out)
+    return gemm_tc(x, w, bias, out_f32=out_f32, out=out, gelu=gelu)
 
 
 def linear_gated(x, w_gate_up):
@@ -1150,10 +1158,10 @@ def qk_norm_store(proj: torch.Tensor, bias, w_q: torch.Tensor, w_k, slots, cache
     (`cache_k` None: nothing is written).  `has_kv` False: the projection holds q only."""
     _on_gpu(proj, bias, w_q, w_k, slots, cache_k, cache_v)
     splits = proj.shape[0] if proj.dim() == 3 else 1
-    tokens, ld = proj.shape[-2], proj.shape[-1]
-    assert proj.dtype == torch.float32 and proj.is_contiguous()
+    tokens, ld = proj.shape[-2], proj.stride(-2)       # a column slice of a wider product will do
+    assert proj.dtype == torch.float32 and proj.stride(-1) == 1 and (splits == 1 or proj.stride(0) == tokens * ld)
     need = n_q * dim + (n_kv * (dim + vdim) if has_kv else 0)
-    assert ld >= need and w_q.numel() == n_q * dim and (not has_kv or w_k.numel() == n_kv * dim)
+    assert proj.shape[-1] >= need and w_q.numel() == n_q * dim and (not has_kv or w_k.numel() == n_kv * dim)
     assert bias is None or (bias.numel() >= need and bias.dtype == w_q.dtype)
     dt = w_q.dtype
     page_size = num_pages = 0
@@ -1176,9 +1184,10 @@ def head_gate(attn: torch.Tensor, proj: torch.Tensor, gate_at: int, per_head: bo
     column slice of a wider buffer."""
     _on_gpu(attn, proj, out)
     splits = proj.shape[0] if proj.dim() == 3 else 1
-    tokens, ld = proj.shape[-2], proj.shape[-1]
-    assert proj.dtype == torch.float32 and proj.is_contiguous() and attn.stride(1) == 1 and attn.shape[0] == tokens
-    assert ld >= gate_at + (n_q if per_head else n_q * vdim)
+    tokens, ld = proj.shape[-2], proj.stride(-2)
+    assert proj.dtype == torch.float32 and proj.stride(-1) == 1 and (splits == 1 or proj.stride(0) == tokens * ld)
+    assert attn.stride(1) == 1 and attn.shape[0] == tokens
+    assert proj.shape[-1] >= gate_at + (n_q if per_head else n_q * vdim)
     if out is None:
         out = torch.empty((tokens, n_q * vdim), dtype=attn.dtype, device=attn.device)
     assert out.dtype == attn.dtype and out.stride(1) == 1 and out.shape == (tokens, n_q * vdim)
@@ -1241,8 +1250,8 @@ def ssm_prepare(proj: torch.Tensor, conv_at: int, dt_at: int, channels: int, tap
     `write` then takes the request's last inputs) with bias and SiLU; columns [dt_at, dt_at + heads) give
     dt = softplus(. + dt_bias) and the decay exp(-exp(a_log) * dt).  Returns (convolved, dt, decay), 32-bit."""
     _on_gpu(proj, taps_w, taps_b, dt_bias, a_log, kept)
-    tokens, ld = proj.shape
-    assert proj.dtype == torch.float32 and proj.is_contiguous() and ld >= max(conv_at + channels, dt_at + heads)
+    tokens, ld = proj.shape[0], proj.stride(0)
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= max(conv_at + channels, dt_at + heads)
     assert taps_w.shape == (channels, taps) and taps_w.is_contiguous() and taps_b.numel() == channels
     assert dt_bias.numel() == heads and a_log.numel() == heads
     assert all(t.dtype == taps_w.dtype for t in (taps_b, dt_bias, a_log))

@@ -191,8 +191,11 @@ class NormedSublayersBlock(Block):
         if self.ffn is not None:
             n2 = self.norms[1]
             with scoped_range(self.ffn_range):
-                f = self.ffn.forward(x if h is None else h, ctx)
-                h = ops.stream_norm_add(x, f, n2.weight, n2.eps, copy=self.dtype != torch.float32)
+                if hasattr(self.ffn, "forward_open"):      # the bias joins the partial products' sum here
+                    f, bias = self.ffn.forward_open(x if h is None else h, ctx)
+                else:
+                    f, bias = self.ffn.forward(x if h is None else h, ctx), None
+                h = ops.stream_norm_add(x, f, n2.weight, n2.eps, bias=bias, copy=self.dtype != torch.float32)
         return x, RoundedStream(x if h is None else h)
 
 

@@ -47,10 +47,12 @@ class DecayLinearAttention(Mixer):
         self.eps = float(spec["eps"])
         self.out_width = self.heads * self.vdim
 
-    def forward_inner(self, x, ctx: StepContext, cache: CacheView, out=None, mult: float = 1.0):
-        """The normed, gated heads side by side [tokens, heads * vdim], times `mult`, in the storage type."""
+    def forward_inner(self, x, ctx: StepContext, cache: CacheView, out=None, mult: float = 1.0, proj=None):
+        """The normed, gated heads side by side [tokens, heads * vdim], times `mult`, in the storage type.  `proj`:
+        the whole 32-bit product of x with `w_in`, where the caller has formed it already."""
         hd, hv = self.heads * self.dim, self.heads * self.vdim
-        proj = ops.linear(x, self.w_in, None, out_f32=True)
+        if proj is None:
+            proj = ops.linear(x, self.w_in, None, out_f32=True)
         o = ops.decay_scan(proj[:, :hd], proj[:, hd: 2 * hd], proj[:, 2 * hd: 2 * hd + hv], cache.state, ctx, self.heads,
                            self.heads, self.dim, self.vdim, a_head=self.decay, silu=True, write=cache.write)
         return ops.gated_norm(o, proj[:, 2 * hd + hv:], self.norm_weight, self.eps, mult=mult, out=out)
@@ -114,9 +116,10 @@ class StateSpaceMixer(Mixer):
         self.w_o = w("o").contiguous()
         self.out_width = self.inner
 
-    def forward_inner(self, x, ctx: StepContext, cache: CacheView, out=None, mult: float = 1.0):
+    def forward_inner(self, x, ctx: StepContext, cache: CacheView, out=None, mult: float = 1.0, proj=None):
         inner, gn = self.inner, self.gn
-        proj = ops.linear(x, self.w_in, None, out_f32=True)
+        if proj is None:
+            proj = ops.linear(x, self.w_in, None, out_f32=True)
         state, kept = cache.part(0), cache.part(1)
         conv, dt, decay = ops.ssm_prepare(proj, inner, 2 * inner + 2 * gn, self.channels, self.taps, self.heads,
                                           self.conv_w, self.conv_b, self.dt_bias, self.a_log, kept.state, ctx,
@@ -134,10 +137,11 @@ class StateSpaceMixer(Mixer):
 class SideBySide(Mixer):
     """Several mixers that read the same input, their results summed with a constant each:
     sum_i c_i * mixer_i(h).  `parts` is a tuple of (mixer spec, c_i).  Each mixer keeps its own cache
-    (`CacheParts`, in the order of `parts`).  Mixers that can leave the input of their output projection in a
-    caller's buffer (`forward_inner`, `w_o`, `out_width`) share one projection: their inner results, each
-    times its constant, lie side by side and meet the output matrices side by side, so the sum is formed
-    inside one product."""
+    (`CacheParts`, in the order of `parts`).  Mixers that take the product of the input with their `w_in` from
+    the caller and leave the input of their output projection in a caller's buffer (`forward_inner`, `w_in`,
+    `w_o`, `out_width`) share both products: one matrix of all their input rows meets h once, and their inner
+    results, each times its constant, lie side by side and meet the output matrices side by side, so the
+    weighted sum is formed inside one product."""
 
     @classmethod
     def _children(cls, spec):
@@ -163,16 +167,20 @@ class SideBySide(Mixer):
         self.decode_graph_safe = all(getattr(m, "decode_graph_safe", False) for m, _ in self.mixers)
         self.shared = all(hasattr(m, "forward_inner") for m, _ in self.mixers)
         if self.shared:
+            self.w_in = torch.cat([m.w_in for m, _ in self.mixers], dim=0).contiguous()
+            self.in_widths = [m.w_in.shape[0] for m, _ in self.mixers]
             self.w_o = torch.cat([m.w_o for m, _ in self.mixers], dim=1).contiguous()
             self.widths = [m.out_width for m, _ in self.mixers]
 
     def forward(self, x, ctx: StepContext, cache: CacheView):
         if self.shared:
+            proj = ops.linear(x, self.w_in, None, out_f32=True)
             inner = torch.empty((x.shape[0], sum(self.widths)), dtype=self.dtype, device=x.device)
-            at = 0
+            at = at_in = 0
             for i, (mixer, c) in enumerate(self.mixers):
-                mixer.forward_inner(x, ctx, cache.part(i), out=inner[:, at: at + self.widths[i]], mult=c)
-                at += self.widths[i]
+                mixer.forward_inner(x, ctx, cache.part(i), out=inner[:, at: at + self.widths[i]], mult=c,
+                                    proj=proj[:, at_in: at_in + self.in_widths[i]])
+                at, at_in = at + self.widths[i], at_in + self.in_widths[i]
             return ops.linear(inner, self.w_o, None, out_f32=True, allow_partial=True)
         total, c_total = None, 1.0
         for i, (mixer, c) in enumerate(self.mixers):

@@ -83,5 +83,11 @@ class DenseMLP(FeedForward):
         act = ops.linear(x, self.w_up, self.b_up, act="gelu_tanh")
         return ops.linear(act, self.w_down, self.b_down, out_f32=self.out_f32)
 
+    def forward_open(self, x, ctx):
+        """(the down product without its bias, whole or as 32-bit split-K partial products; the bias or None):
+        for a consumer that sums partial products and adds the bias in its own pass."""
+        act = ops.linear(x, self.w_up, self.b_up, act="gelu_tanh")
+        return ops.linear(act, self.w_down, None, out_f32=True, allow_partial=True), self.b_down
+
 
 register_part("feed_forward", "dense_mlp", DenseMLP)

@@ -81,10 +81,12 @@ class GatedNormAttention(Mixer):
         self.w_o = w("o").contiguous()
         self.out_width = self.n_q * self.vdim
 
-    def forward_inner(self, x: torch.Tensor, ctx: StepContext, cache: CacheView, out=None, mult: float = 1.0):
-        """The gated heads side by side [tokens, heads * vdim], times `mult`, in the storage type."""
+    def forward_inner(self, x: torch.Tensor, ctx: StepContext, cache: CacheView, out=None, mult: float = 1.0, proj=None):
+        """The gated heads side by side [tokens, heads * vdim], times `mult`, in the storage type.  `proj`: the
+        32-bit product of x with `w_in`, where the caller has formed it already (as columns of a wider one)."""
         group = ctx.groups[cache.group]
-        proj = ops.linear(x, self.w_in, None, out_f32=True, allow_partial=True)
+        if proj is None:
+            proj = ops.linear(x, self.w_in, None, out_f32=True, allow_partial=True)
         write = cache.write and self.own_kv
         q = ops.qk_norm_store(proj, self.bias, self.norm_q, self.norm_k, group.row_slot if write else None,
                               cache.k if write else None, cache.v if write else None, self.n_q, self.n_kv, self.dim,

@@ -68,6 +68,27 @@ def test_stream_operators_against_numpy():
         assert np.abs(_np(ops.gelu_tanh_(z.clone())) - ref).max() < (1e-6 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize("tokens,n_out,k", [(3, 200, 64), (70, 96, 320), (300, 520, 128), (4100, 512, 2048),
+                                            (9, 50, 36), (200, 30, 100)])
+def test_gelu_in_the_products_epilogue(tokens, n_out, k):
+    """The activation as the epilogue of the up product (both orientations of the tensor-core kernel, the
+    kernel on pairs of SMs, and the plain kernel for rows of no 16-byte multiple and in 32-bit) against the
+    product followed by the activation kernel, and against NumPy."""
+    torch = _torch()
+    from llm_inference_lab_b200.kernels import ops
+    rng = np.random.default_rng(tokens)
+    for dtype in (torch.bfloat16, torch.float32):
+        x, w, b = _t(rng.standard_normal((tokens, k)), dtype), _t(rng.standard_normal((n_out, k)) / np.sqrt(k), dtype), \
+            _t(rng.standard_normal(n_out), dtype)
+        fused = ops.linear(x, w, b, act="gelu_tanh")
+        ref = pr.gelu_tanh(_np(x) @ _np(w).T + _np(b))
+        assert fused.dtype == dtype and np.abs(_np(fused) - ref).max() < (2e-2 if dtype == torch.bfloat16 else 1e-5)
+        two = ops.gelu_tanh_(ops.linear(x, w, b, out_f32=True)).to(dtype)     # one rounding, as in the epilogue
+        assert torch.equal(fused, two)
+    with pytest.raises(ops.KernelError):
+        ops.linear(x, w, b, act="relu")
+
+
 @pytest.mark.parametrize("dims", [(3, 1, 16, 24), (2, 2, 40, 8), (4, 2, 64, 64)])
 def test_whole_projection_norms_cache_store_and_gates(dims):
     """q and k normed over all heads at once (not head by head), heads stored with zero padding, k and v in the
