@@ -601,6 +601,175 @@ def run_arch_sogulix(args):
     return 0
 
 
+# ----------------------------------------------------------------------------------------
+# --arch ritizen: the Ritizen design beside Sogulix and Qwen2 at equal layer sizes (random weights)
+# ----------------------------------------------------------------------------------------
+RITIZEN_SHAPES = {
+    # width, feed-forward and vocabulary of the Qwen2.5 shape of the same name; attention heads as there;
+    # the recurrent mixers sized like the attention (state-space: inner = 2 x width)
+    "0.5B": dict(heads=14, kv_heads=2, dim=64, vdim=64, chunk=1024, lin_heads=14, lin_dim=64, lin_vdim=64,
+                 ssm_heads=28, ssm_vdim=64, ssm_state=64, ssm_groups=2, taps=4, norm_groups=2),
+    "1.5B": dict(heads=12, kv_heads=2, dim=128, vdim=128, chunk=2048, lin_heads=12, lin_dim=128, lin_vdim=128,
+                 ssm_heads=24, ssm_vdim=128, ssm_state=128, ssm_groups=2, taps=4, norm_groups=2),
+}
+
+
+def ritizen_config(shape, layers):
+    """Layers in the order attention, attention on the first one's keys and values, state-space, side by side."""
+    q, m = SHAPES[shape], RITIZEN_SHAPES[shape]
+    mlp = {"kind": "dense", "ff": q["intermediate_size"]}
+    att = {"heads": m["heads"], "kv_heads": m["kv_heads"], "dim": m["dim"], "vdim": m["vdim"], "scale": m["dim"] ** -0.5}
+    decay = [1.0 - 2.0 ** -(2 + 6 * h / max(1, m["lin_heads"] - 1)) for h in range(m["lin_heads"])]
+    kinds = [
+        lambda i: {"type": "attention", "mixer": dict(att), "mlp": mlp},
+        lambda i: {"type": "attention", "mixer": dict(att, kv_from=i - 1), "mlp": mlp},
+        lambda i: {"type": "mamba2", "mlp": None,
+                   "mixer": {"heads": m["ssm_heads"], "vdim": m["ssm_vdim"], "state": m["ssm_state"],
+                             "groups": m["ssm_groups"], "conv": m["taps"], "norm_groups": m["norm_groups"]}},
+        lambda i: {"type": "parallel", "mlp": mlp,
+                   "mixer": {"left": dict(att, mask={"size": m["chunk"]}), "left_scale": 0.6, "right_scale": 1.1,
+                             "right": {"heads": m["lin_heads"], "dim": m["lin_dim"], "vdim": m["lin_vdim"],
+                                       "decay": decay}}},
+    ]
+    return {"architecture": "Ritizen", "vocab": q["vocab_size"], "width": q["hidden_size"], "max_positions": 4096,
+            "norm": {"eps": 1e-6}, "layers": [kinds[i % 4](i) for i in range(layers)]}
+
+
+def kernel_points_ritizen(shape, batch, ctx_len, prefill_tokens, pk):
+    """The Ritizen design's own kernels beside the like kernels of Sogulix (the recurrence, the stream's sum)
+    and of Qwen2 (attention, the rotation with its cache write, add + norm) at the shape's sizes, each alone
+    between CUDA events with L2 flushed: milliseconds and the fraction of the roofline (measured copy bandwidth
+    for kernels that stream, measured bf16 product rate for the attention kernels of a prompt)."""
+    import torch
+    from llm_inference_lab_b200.kernels import ops
+
+    dev = torch.device("cuda:0")
+    q, m, sg = SHAPES[shape], RITIZEN_SHAPES[shape], SOGULIX_SHAPES[shape]
+    width = q["hidden_size"]
+    flush = torch.zeros((160 << 20,), dtype=torch.int16, device=dev)
+    bw, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    rows = {}
+
+    def record(name, ms, nbytes=None, flops=None):
+        entry = {"ms": round(ms, 4)}
+        if nbytes is not None:
+            entry.update(gbs=round(nbytes / (ms / 1e3) / 1e9, 1), frac_hbm=round(nbytes / (ms / 1e3) / bw, 4))
+        if flops is not None:
+            entry.update(tflops=round(flops / (ms / 1e3) / 1e12, 2), frac_bf16=round(flops / (ms / 1e3) / tf, 4))
+        rows[name] = entry
+
+    bf = lambda *s: torch.randn(*s, device=dev).to(torch.bfloat16)  # noqa: E731
+    f32 = lambda *s: torch.randn(*s, device=dev)  # noqa: E731
+    for label, q_lens, pos0 in (("prefill", [prefill_tokens], [0]), ("decode", [1] * batch, [ctx_len] * batch)):
+        T, B = sum(q_lens), len(q_lens)
+        ctx, pages = bench_ctx(q_lens, pos0, PAGE_SIZE, dev)
+        # the recurrence with a fixed decay per head: reads q, k, v (32-bit), writes o, the state in and out
+        H, N, V = m["lin_heads"], m["lin_dim"], m["lin_vdim"]
+        proj = f32(T, 2 * H * N + 2 * H * V)
+        state = torch.zeros(B, H, N, V, device=dev)
+        decay = torch.full((H,), 0.97, device=dev)
+        ms = timed(lambda: ops.decay_scan(proj[:, : H * N], proj[:, H * N: 2 * H * N], proj[:, 2 * H * N: 2 * H * N + H * V],
+                                          state, ctx, H, H, N, V, a_head=decay, silu=True), flush=flush)
+        record(f"decay_scan fixed decay {label}", ms, nbytes=T * (2 * H * N + 2 * H * V) * 4 + 2 * state.numel() * 4,
+               flops=None if label == "decode" else 4.0 * T * H * N * V)
+        # the same recurrence with a decay and a key scale per token (state-space), q and k shared by groups
+        H2, N2, V2, G2 = m["ssm_heads"], m["ssm_state"], m["ssm_vdim"], m["ssm_groups"]
+        conv = f32(T, H2 * V2 + 2 * G2 * N2)
+        a_tok, s_tok = torch.rand(T, H2, device=dev), torch.rand(T, H2, device=dev)
+        state2 = torch.zeros(B, H2, N2, V2, device=dev)
+        ms = timed(lambda: ops.decay_scan(conv[:, H2 * V2 + G2 * N2:], conv[:, H2 * V2: H2 * V2 + G2 * N2], conv[:, : H2 * V2],
+                                          state2, ctx, H2, G2, N2, V2, a_tok=a_tok, s_tok=s_tok), flush=flush)
+        record(f"decay_scan decay per token {label}", ms,
+               nbytes=T * (2 * G2 * N2 + 2 * H2 * V2 + 2 * H2) * 4 + 2 * state2.numel() * 4,
+               flops=None if label == "decode" else 4.0 * T * H2 * N2 * V2)
+        # Sogulix's recurrence (the generalized delta rule) at its shape of the same name
+        Hs, Ds = sg["heads"], sg["dim"]
+        sproj, dpre = f32(T, 5 * Hs * Ds + 64), f32(T, Hs * Ds)
+        sstate = torch.zeros(B, Hs, Ds, Ds, device=dev)
+        ones = bf(Hs * Ds)
+        ms = timed(lambda: ops.delta_rule(sproj, dpre, ones, ones, ones, sstate, ctx, Hs, Ds, 1e-6, 0.6), flush=flush)
+        record(f"sogulix delta_rule {label}", ms, nbytes=T * Hs * Ds * (6 * 4 + 2) + 2 * sstate.numel() * 4,
+               flops=None if label == "decode" else 8.0 * T * Hs * Ds * Ds)
+        # the state-space mixer's preparation and the gate + norm that close both recurrent mixers
+        inner, gn = H2 * V2, G2 * N2
+        sproj2 = f32(T, 2 * inner + 2 * gn + H2)
+        kept = torch.zeros(B, m["taps"] - 1, inner + 2 * gn, device=dev)
+        tw, tb, hb = bf(inner + 2 * gn, m["taps"]), bf(inner + 2 * gn), bf(H2)
+        ms = timed(lambda: ops.ssm_prepare(sproj2, inner, 2 * inner + 2 * gn, inner + 2 * gn, m["taps"], H2, tw, tb, hb, hb,
+                                           kept, ctx), flush=flush)
+        record(f"ssm_prepare {label}", ms, nbytes=T * ((inner + 2 * gn + H2) * 4 + (inner + 2 * gn + 2 * H2) * 4))
+        o, wn = f32(T, inner), bf(inner)
+        ms = timed(lambda: ops.gated_norm(o, sproj2[:, :inner], wn, 1e-6, parts=m["norm_groups"], gate_first=True, skip=hb,
+                                          x=conv[:, :inner], head_size=V2), flush=flush)
+        record(f"gated_norm {label}", ms, nbytes=T * inner * (4 + 4 + 4 + 2))
+        # attention: norms over the whole projections with the paged store, the kernels with a chunk mask, the gate
+        nq, nkv, D, Vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        hd = ops.padded_head(D, Vd)
+        ck, cv = bf(pages, nkv, PAGE_SIZE, hd), bf(pages, nkv, PAGE_SIZE, hd)
+        wide = nq * D + nkv * (D + Vd) + nq * Vd
+        aproj = f32(T, wide)
+        ab, wq, wk = bf(nq * D + nkv * (D + Vd)), bf(nq * D), bf(nkv * D)
+        ms = timed(lambda: ops.qk_norm_store(aproj, ab, wq, wk, ctx.groups[0].row_slot, ck, cv, nq, nkv, D, Vd, hd, 1e-6),
+                   flush=flush)
+        record(f"qk_norm_store {label}", ms, nbytes=T * ((nq * D + nkv * (D + Vd)) * 4 + (nq + 2 * nkv) * hd * 2))
+        qq = bf(T, nq * hd)
+        all_pairs = sum(sum(p + i + 1 for i in range(n)) for p, n in zip(pos0, q_lens))
+        chunk = m["chunk"]
+        in_chunk = sum(sum((p + i) % chunk + 1 for i in range(n)) for p, n in zip(pos0, q_lens))
+        for name, ch, pairs, keys in (("causal", 0, all_pairs, sum(p + n for p, n in zip(pos0, q_lens))),
+                                      ("chunked", chunk, in_chunk,
+                                       sum(min(p + n, (p + n - 1) % chunk + n) for p, n in zip(pos0, q_lens)))):
+            ms = timed(lambda: ops.attention(qq, ck, cv, ctx, ctx.groups[0], nq, nkv, hd, 0, D ** -0.5, chunk=ch), flush=flush)
+            record(f"attention {name} {label}", ms, nbytes=keys * 2 * nkv * hd * 2 + 2 * T * nq * hd * 2,
+                   flops=4.0 * pairs * nq * hd)
+        attn = bf(T, nq * hd)
+        ms = timed(lambda: ops.head_gate(attn, aproj, nq * D + nkv * (D + Vd), False, nq, Vd, hd), flush=flush)
+        record(f"head_gate {label}", ms, nbytes=T * nq * Vd * (2 + 4 + 2))
+        # Qwen2's rotation with its cache write, at the same heads
+        d = q["hidden_size"] // q["num_attention_heads"]
+        qn, qkvh = q["num_attention_heads"], q["num_key_value_heads"]
+        if ops.attention_tc_supported(d):
+            qkv = bf(T, (qn + 2 * qkvh) * d)
+            ck2, cv2 = bf(pages, qkvh, PAGE_SIZE, d), bf(pages, qkvh, PAGE_SIZE, d)
+            inv = torch.rand(d // 2, device=dev)
+            ms = timed(lambda: ops.rope_kv_write(qkv, ctx.row_pos, inv, d, ctx.groups[0].row_slot, ck2, cv2, qn, qkvh, d),
+                       flush=flush)
+            record(f"qwen2 rotation + cache write {label}", ms, nbytes=T * (qn + 2 * qkvh) * d * 2 * 2)
+        # the sum that closes a sublayer: x += norm(product), with the rounded copy
+        x, a, w1 = f32(T, width), f32(T, width), bf(width)
+        ms = timed(lambda: ops.stream_norm_add(x, a, w1, 1e-6, copy=True), flush=flush)
+        record(f"stream_norm_add {label}", ms, nbytes=T * width * (4 + 4 + 4 + 2))
+        fsum = f32(T, width)
+        ms = timed(lambda: ops.stream_add(x, a, w1, fsum, w1, 0.5), flush=flush)
+        record(f"sogulix stream add {label}", ms, nbytes=T * width * 16)
+        xb, delta = bf(T, width), bf(T, width)
+        ms = timed(lambda: ops.add_rmsnorm(xb, w1, 1e-6, delta=delta), flush=flush)
+        record(f"qwen2 add + norm {label}", ms, nbytes=T * width * 8)
+    ops.take_device_errors()
+    return rows
+
+
+def run_arch_ritizen(args):
+    shape, layers = args.shape, args.layers or 4
+    pk, pk_src = peaks()
+    qcfg = dict(SHAPES[shape], num_hidden_layers=layers)
+    folders = {"ritizen": arch_folder(ritizen_config(shape, layers), f"ritizen_{shape}_L{layers}"),
+               "sogulix": arch_folder(sogulix_config(shape, layers), f"sogulix_{shape}_L{layers}"),
+               "qwen2": model_folder(SHAPES[shape], layers)}
+    clocks = ClockSampler()
+    with clocks:
+        models = {name: model_points(folder, args.batch, args.prompt_len, PREFILL_TOKENS, 20)
+                  for name, folder in folders.items()}
+        kernels = kernel_points_ritizen(shape, args.batch, args.prompt_len + 512, PREFILL_TOKENS, pk)
+    print(json.dumps({
+        "arch": "ritizen", "beside": ["sogulix", "qwen2"], "shape": shape, "layers": layers, "batch": args.batch,
+        "prompt_len": args.prompt_len, "prefill_tokens": PREFILL_TOKENS, "dtype": "bf16",
+        "data": "synthetic: random weights N(0, 0.02) seed 0", "ritizen_mixers": RITIZEN_SHAPES[shape],
+        "hidden": qcfg["hidden_size"], "intermediate": qcfg["intermediate_size"], "vocab": qcfg["vocab_size"],
+        "models": models, "kernels": kernels, "peaks": dict(pk, source=pk_src), "clocks": clocks.summary()}))
+    return 0
+
+
 def kv_bytes_per_token(cfg, layers):
     d = cfg["hidden_size"] // cfg["num_attention_heads"]
     return 2 * layers * 2 * cfg["num_key_value_heads"] * d
@@ -629,10 +798,11 @@ def main() -> int:
     ap.add_argument("--stack-stamps", action="store_true",
                     help="run a few eager decode steps with the decode stack's in-kernel clock on and print what "
                          "each kind of phase took")
-    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "sogulix"],
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "sogulix", "ritizen"],
                     help="sogulix: instead of the headline run, prefill and decode throughput of the Sogulix design "
                          "beside Qwen2 at the layer sizes of --shape (0.5B or 1.5B; --layers, default 4), and each "
-                         "of its kernels beside Qwen2's like kernel; prints its own line")
+                         "of its kernels beside Qwen2's like kernel; prints its own line.  ritizen: the same for the "
+                         "Ritizen design, beside Sogulix and Qwen2")
     ap.add_argument("--only-prefill", type=int, default=0, metavar="TOKENS",
                     help="run only a prefill of TOKENS tokens a few times and print its time (for profiling)")
     args = ap.parse_args()
@@ -664,6 +834,11 @@ def main() -> int:
             ap.error("--arch sogulix knows the shapes " + ", ".join(sorted(SOGULIX_SHAPES)))
         args.layers = 0 if args.layers == cfg["num_hidden_layers"] else args.layers
         return run_arch_sogulix(args)
+    if args.arch == "ritizen":
+        if args.shape not in RITIZEN_SHAPES:
+            ap.error("--arch ritizen knows the shapes " + ", ".join(sorted(RITIZEN_SHAPES)))
+        args.layers = 0 if args.layers == cfg["num_hidden_layers"] else args.layers
+        return run_arch_ritizen(args)
     folder = model_folder(cfg, args.layers)
     pk, pk_src = peaks()
     if args.serve:

@@ -28,11 +28,18 @@ constexpr int SCAN_P = 4;     // threads that share one column of the state
 constexpr int SCAN_CT = 16;   // tokens staged per chunk
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+// SiLU by the hardware's 2^x and reciprocal approximations (relative error about 2^-21, as the attention
+// kernels' softmax has it): a few instructions instead of the seventy of the exact exponential and division,
+// which the recurrence's helpers would otherwise spend longer on than its walkers on their chunk.
+__device__ __forceinline__ float silu_quick(float z) { return __fdividef(z, 1.0f + fast_exp2(-1.4426950408889634f * z)); }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait_group() {
@@ -55,21 +62,38 @@ struct ScanParams {
   const int* q_start;
   const int* state_slot;
   int n_slots, H, G, N, V, act, write;
+  int vec;               // q, k, v rows may be copied 16 bytes at a time
 };
 
-// grid (slices of V, heads, requests); block SCAN_P * Vs threads: thread (j, p) keeps rows p, p + 4, ... of
-// column slice * Vs + j of the state in registers.  The rows of a chunk of tokens arrive by cp.async in the
-// buffer that is not being walked.
+// grid (slices of V, heads, requests); block 2 * SCAN_P * Vs threads in two halves.
+//
+// Walkers (the first SCAN_P * Vs threads): thread (j, part) keeps rows part * R .. part * R + R - 1 of column
+// slice * Vs + j of the state in registers (R a multiple of 4: the rows' keys and queries come from shared
+// memory four at a time; the four threads' shares of a token's keys lie R + 4 floats apart, which spreads
+// their 16-byte loads over the banks).  A token costs a walker 2 R multiply-adds behind R / 2 loads; the four
+// walkers of a column add their shares of the output by two shuffles.  The next token's keys, queries and
+// value are loaded before the current token's arithmetic (up to R = 16; beyond, registers do not allow it).
+// The walk is one dependent chain per request and head: its time is the number of tokens times that step,
+// whatever the number of CTAs, so nothing else may sit on it.
+//
+// Helpers (the other half) keep everything else off that chain: while the walkers are on chunk c (16 tokens),
+// the helpers apply the SiLU to chunk c + 1, whose rows their cp.async copies have brought (16 bytes a copy
+// where the operands' addresses allow it: `vec`), and start the copies of chunk c + 2 into the buffer the
+// walkers left one chunk ago.  Three buffers, one barrier of the whole CTA per chunk.
 template <int R>
-__global__ void __launch_bounds__(128) decay_scan_kernel(ScanParams p) {
-  extern __shared__ float smem[];
-  constexpr int NP = SCAN_P * R;                 // key channels with padding
+__global__ void __launch_bounds__(256) decay_scan_kernel(ScanParams p) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int RS = R + 4;                      // floats between two threads' shares of a token's keys
+  constexpr int NP = SCAN_P * RS;                // floats of a token's keys (or queries) in shared memory
+  constexpr bool AHEAD = R <= 16;                // the next token's operands are loaded a token ahead
   pdl_trigger();
-  const int Vs = blockDim.x / SCAN_P;
-  const int tok_floats = 2 * NP + Vs + 2;        // k | q | v | a | s
+  const int walkers = blockDim.x / 2, Vs = walkers / SCAN_P;
+  const int tok_floats = 2 * NP + Vs + 4;        // k | q | v | a | s | (two unused, which keep rows 16-byte aligned)
   const int h = blockIdx.y, r = blockIdx.z, g = h / (p.H / p.G);
-  const int tid = threadIdx.x, j = tid / SCAN_P, part = tid % SCAN_P;
-  const int col = blockIdx.x * Vs + j;
+  const bool helper = threadIdx.x >= walkers;
+  const int tid = helper ? threadIdx.x - walkers : threadIdx.x;      // index within the half
+  const int j = tid / SCAN_P, part = tid % SCAN_P;
+  const int col0 = blockIdx.x * Vs, col = col0 + j;
   const int t0 = p.q_start[r], n_tok = p.q_start[r + 1] - t0;
   const int slot = p.state_slot[r];
   if (n_tok <= 0 || slot == -1) {      // nothing to do, or rows of padding (their output is never read)
@@ -77,88 +101,154 @@ __global__ void __launch_bounds__(128) decay_scan_kernel(ScanParams p) {
     return;
   }
   if (slot < 0 || slot >= p.n_slots) {
-    if (tid == 0) lab_set_error(LAB_ERR_PAGE_RANGE);
+    if (threadIdx.x == 0) lab_set_error(LAB_ERR_PAGE_RANGE);
     pdl_wait();
     return;
   }
-  // padding of the key channels stays zero for the whole walk: the copies never touch it
-  for (int i = tid; i < 2 * SCAN_CT * tok_floats; i += blockDim.x) smem[i] = 0.f;
+  // padding of the key channels and of the columns stays zero for the whole walk: the copies never touch it
+  for (int i = threadIdx.x; i < 3 * SCAN_CT * tok_floats; i += blockDim.x) smem[i] = 0.f;
   __syncthreads();
   pdl_wait();
 
-  float S[R];
-  float* st = p.state + ((size_t)slot * p.H + h) * p.N * p.V;
-#pragma unroll
-  for (int i = 0; i < R; ++i) {
-    const int n = part + SCAN_P * i;
-    S[i] = (n < p.N && col < p.V) ? st[(size_t)n * p.V + col] : 0.f;
-  }
-  const float a_const = p.a_tok == nullptr ? p.a_head[h] : 0.f;
+  const int n_chunks = (n_tok + SCAN_CT - 1) / SCAN_CT;
+  const int v_cols = min(Vs, p.V - col0);
+  auto buffer = [&](int chunk) { return smem + (chunk % 3) * SCAN_CT * tok_floats; };
 
-  auto issue = [&](int chunk, int buf) {
+  // ---- helpers' pieces ----
+  auto at = [](int n) { return (n / R) * RS + (n % R); };      // where key channel n lies within a token's keys
+  // One loop over all of a chunk's copies (tokens x pieces), so that every helper has a few copies in flight
+  // instead of the helpers walking the tokens one after the other.
+  auto issue = [&](int chunk) {
     const int first = chunk * SCAN_CT, cnt = min(SCAN_CT, n_tok - first);
-    float* base = smem + buf * SCAN_CT * tok_floats;
-    const int per = 2 * p.N + Vs + 2;
-    for (int e = tid; e < cnt * per; e += blockDim.x) {
-      const int tt = e / per, c = e - tt * per;
-      const size_t t = (size_t)(t0 + first + tt);
-      float* dst = base + tt * tok_floats;
-      if (c < p.N) cp_async4(dst + c, p.k + t * p.ld_qk + g * p.N + c);
-      else if (c < 2 * p.N) cp_async4(dst + NP + (c - p.N), p.q + t * p.ld_qk + g * p.N + (c - p.N));
-      else if (c < 2 * p.N + Vs) {
-        const int cc = blockIdx.x * Vs + (c - 2 * p.N);
-        if (cc < p.V) cp_async4(dst + 2 * NP + (c - 2 * p.N), p.v + t * p.ld_v + h * p.V + cc);
-      } else if (p.a_tok != nullptr) {
-        const int which = c - 2 * p.N - Vs;
-        const float* src = which == 0 ? p.a_tok : p.s_tok;
-        if (src != nullptr) cp_async4(dst + 2 * NP + Vs + which, src + t * p.ld_a + h);
+    float* base = buffer(chunk);
+    const float* k0 = p.k + (size_t)(t0 + first) * p.ld_qk + g * p.N;
+    const float* q0 = p.q + (size_t)(t0 + first) * p.ld_qk + g * p.N;
+    const float* v0 = p.v + (size_t)(t0 + first) * p.ld_v + h * p.V + col0;
+    if (p.vec) {
+      const int nk = p.N / 4, nv = v_cols / 4, per = 2 * nk + nv;
+      for (int e = tid; e < cnt * per; e += walkers) {
+        const int tt = e / per, c = e - tt * per;
+        float* dst = base + tt * tok_floats;
+        if (c < nk) cp_async16(dst + at(4 * c), k0 + (size_t)tt * p.ld_qk + 4 * c);
+        else if (c < 2 * nk) cp_async16(dst + NP + at(4 * (c - nk)), q0 + (size_t)tt * p.ld_qk + 4 * (c - nk));
+        else cp_async16(dst + 2 * NP + 4 * (c - 2 * nk), v0 + (size_t)tt * p.ld_v + 4 * (c - 2 * nk));
       }
+    } else {
+      const int per = 2 * p.N + v_cols;
+      for (int e = tid; e < cnt * per; e += walkers) {
+        const int tt = e / per, c = e - tt * per;
+        float* dst = base + tt * tok_floats;
+        if (c < p.N) cp_async4(dst + at(c), k0 + (size_t)tt * p.ld_qk + c);
+        else if (c < 2 * p.N) cp_async4(dst + NP + at(c - p.N), q0 + (size_t)tt * p.ld_qk + (c - p.N));
+        else cp_async4(dst + 2 * NP + (c - 2 * p.N), v0 + (size_t)tt * p.ld_v + (c - 2 * p.N));
+      }
+    }
+    if (p.a_tok != nullptr && tid < 2 * cnt) {      // a token's decay and key scale: one helper each
+      const int tt = tid >> 1, which = tid & 1;
+      const float* src = which == 0 ? p.a_tok : p.s_tok;
+      if (src != nullptr)
+        cp_async4(base + tt * tok_floats + 2 * NP + Vs + which, src + (size_t)(t0 + first + tt) * p.ld_a + h);
+    }
+  };
+  // after the copies of `chunk` have landed for every helper: SiLU of q, k and v, once per element
+  auto finish = [&](int chunk) {
+    asm volatile("bar.sync 1, %0;" ::"r"(walkers) : "memory");      // the helpers alone
+    if (!p.act) return;
+    const int cnt = min(SCAN_CT, n_tok - chunk * SCAN_CT), per = (2 * NP + Vs) / 4;
+    float* base = buffer(chunk);
+    for (int e = tid; e < cnt * per; e += walkers) {
+      const int tt = e / per, c = e - tt * per;
+      float4* at4 = reinterpret_cast<float4*>(base + tt * tok_floats) + c;
+      float4 z = *at4;
+      z.x = silu_quick(z.x), z.y = silu_quick(z.y), z.z = silu_quick(z.z), z.w = silu_quick(z.w);
+      *at4 = z;
     }
   };
 
-  const int n_chunks = (n_tok + SCAN_CT - 1) / SCAN_CT;
-  issue(0, 0);
-  cp_async_commit_group();
-  for (int c = 0; c < n_chunks; ++c) {
-    const int buf = c & 1;
-    if (c + 1 < n_chunks) issue(c + 1, buf ^ 1);
+  float S[R];
+  float* st = p.state + ((size_t)slot * p.H + h) * p.N * p.V;
+  float a_const = 0.f;
+  if (helper) {
+    issue(0);
+    cp_async_commit_group();
+    if (n_chunks > 1) issue(1);
     cp_async_commit_group();
     cp_async_wait_group<1>();
-    __syncthreads();
-    const int cnt = min(SCAN_CT, n_tok - c * SCAN_CT);
-    float* base = smem + buf * SCAN_CT * tok_floats;
-    if (p.act) {      // SiLU of q, k and v, once per element
-      const int per = 2 * NP + Vs;
-      for (int e = tid; e < cnt * per; e += blockDim.x) {
-        const int tt = e / per, cc = e - tt * per;
-        float* at = base + tt * tok_floats + cc;
-        *at = silu_f(*at);
-      }
-      __syncthreads();
-    }
-    for (int tt = 0; tt < cnt; ++tt) {
-      const float* tok = base + tt * tok_floats;
-      const float a = p.a_tok != nullptr ? tok[2 * NP + Vs] : a_const;
-      float vj = tok[2 * NP + j];
-      if (p.s_tok != nullptr) vj *= tok[2 * NP + Vs + 1];
-      float acc = 0.f;
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        const int n = part + SCAN_P * i;
-        S[i] = fmaf(a, S[i], tok[n] * vj);
-        acc = fmaf(S[i], tok[NP + n], acc);
-      }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      if (part == 0 && col < p.V) p.out[(size_t)(t0 + c * SCAN_CT + tt) * p.ld_o + h * p.V + col] = acc;
-    }
-    __syncthreads();      // the buffer is refilled by the next iteration's copies
-  }
-  cp_async_wait_group<0>();
-  if (p.write) {
+    finish(0);
+  } else {
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      const int n = part + SCAN_P * i;
+      const int n = part * R + i;
+      S[i] = (n < p.N && col < p.V) ? st[(size_t)n * p.V + col] : 0.f;
+    }
+    if (p.a_tok == nullptr) a_const = p.a_head[h];
+  }
+  __syncthreads();
+
+  for (int c = 0; c < n_chunks; ++c) {
+    if (helper) {
+      if (c + 2 < n_chunks) issue(c + 2);      // into the buffer the walkers left at the last barrier
+      cp_async_commit_group();
+      if (c + 1 < n_chunks) {
+        cp_async_wait_group<1>();              // all but the copies just started: chunk c + 1 is here
+        finish(c + 1);
+      }
+    } else {
+      const int cnt = min(SCAN_CT, n_tok - c * SCAN_CT);
+      const float* base = buffer(c);
+      float* out = p.out + (size_t)(t0 + c * SCAN_CT) * p.ld_o + h * p.V + col;
+      float4 kk[R / 4], qq[R / 4];
+      float a, vj;
+      auto load = [&](int tt, float4* k_to, float4* q_to, float& a_to, float& v_to) {
+        const float* tok = base + tt * tok_floats;
+        const float4* k4 = reinterpret_cast<const float4*>(tok + part * RS);
+        const float4* q4 = reinterpret_cast<const float4*>(tok + NP + part * RS);
+#pragma unroll
+        for (int i = 0; i < R / 4; ++i) k_to[i] = k4[i], q_to[i] = q4[i];
+        a_to = p.a_tok != nullptr ? tok[2 * NP + Vs] : a_const;
+        v_to = tok[2 * NP + j];
+        if (p.s_tok != nullptr) v_to *= tok[2 * NP + Vs + 1];
+      };
+      if (AHEAD) load(0, kk, qq, a, vj);
+      for (int tt = 0; tt < cnt; ++tt) {
+        float4 kn[AHEAD ? R / 4 : 1], qn[AHEAD ? R / 4 : 1];
+        float an = 0.f, vn = 0.f;
+        if (AHEAD) {
+          if (tt + 1 < cnt) load(tt + 1, kn, qn, an, vn);
+        } else {
+          load(tt, kk, qq, a, vj);
+        }
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < R / 4; ++i) {
+          S[4 * i + 0] = fmaf(a, S[4 * i + 0], kk[i].x * vj);
+          S[4 * i + 1] = fmaf(a, S[4 * i + 1], kk[i].y * vj);
+          S[4 * i + 2] = fmaf(a, S[4 * i + 2], kk[i].z * vj);
+          S[4 * i + 3] = fmaf(a, S[4 * i + 3], kk[i].w * vj);
+          acc[0] = fmaf(S[4 * i + 0], qq[i].x, acc[0]);
+          acc[1] = fmaf(S[4 * i + 1], qq[i].y, acc[1]);
+          acc[2] = fmaf(S[4 * i + 2], qq[i].z, acc[2]);
+          acc[3] = fmaf(S[4 * i + 3], qq[i].w, acc[3]);
+        }
+        float total = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        total += __shfl_xor_sync(0xffffffffu, total, 1);
+        total += __shfl_xor_sync(0xffffffffu, total, 2);
+        if (part == 0 && col < p.V) out[(size_t)tt * p.ld_o] = total;
+        if (AHEAD) {
+#pragma unroll
+          for (int i = 0; i < R / 4; ++i) kk[i] = kn[i], qq[i] = qn[i];
+          a = an, vj = vn;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (helper) {
+    cp_async_wait_group<0>();
+  } else if (p.write) {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int n = part * R + i;
       if (n < p.N && col < p.V) st[(size_t)n * p.V + col] = S[i];
     }
   }
@@ -274,11 +364,11 @@ __global__ void __launch_bounds__(kThreads) gated_norm_kernel(T* __restrict__ ou
 
 template <int R>
 int launch_scan(const ScanParams& p, int requests, int vs, cudaStream_t stream) {
-  const size_t smem = (size_t)2 * SCAN_CT * (2 * SCAN_P * R + vs + 2) * sizeof(float);
+  const size_t smem = (size_t)3 * SCAN_CT * (2 * SCAN_P * (R + 4) + vs + 4) * sizeof(float);
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(decay_scan_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid((p.V + vs - 1) / vs, p.H, requests);
-  return (int)lab_launch(decay_scan_kernel<R>, grid, dim3(SCAN_P * vs), smem, stream, p);
+  return (int)lab_launch(decay_scan_kernel<R>, grid, dim3(2 * SCAN_P * vs), smem, stream, p);
 }
 
 }  // namespace
@@ -298,6 +388,9 @@ LAB_EXPORT int lab_decay_scan(float* out, int ld_o, const float* q, const float*
   p.out = out; p.ld_o = ld_o; p.q = q; p.k = k; p.ld_qk = ld_qk; p.v = v; p.ld_v = ld_v; p.a_tok = a_tok;
   p.s_tok = s_tok; p.ld_a = ld_a; p.a_head = a_head; p.state = state; p.q_start = q_start; p.state_slot = state_slot;
   p.n_slots = n_slots; p.H = H; p.G = G; p.N = N; p.V = V; p.act = act; p.write = write;
+  // 16-byte copies: every row of q, k and v, and every head's and slice's start in it, on a 16-byte boundary
+  p.vec = N % 4 == 0 && V % 4 == 0 && ld_qk % 4 == 0 && ld_v % 4 == 0 &&
+          ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v)) & 15) == 0;
   if (N <= SCAN_P * 4) return launch_scan<4>(p, requests, vs, stream);
   if (N <= SCAN_P * 8) return launch_scan<8>(p, requests, vs, stream);
   if (N <= SCAN_P * 16) return launch_scan<16>(p, requests, vs, stream);

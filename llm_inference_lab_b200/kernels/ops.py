@@ -1230,9 +1230,14 @@ def decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.T
     if not decay_scan_supported(keys):
         raise KernelError(f"decay_scan: {keys} key channels are outside what the recurrence kernel takes (1..256)")
     out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=v.device)
-    # columns of the state per CTA: narrow slices when a step has few (request, head) pairs, so that more SMs work
+    # Columns of the state per CTA.  Over a portion of a prompt the walk is one dependent chain per request and
+    # head whatever the slice, and wide slices stage the keys and queries fewer times.  A step of single tokens
+    # only reads and writes the state: narrow slices when it has few (request, head) pairs, so that more SMs work.
     pairs = ctx.n_requests * heads
-    vs = 32 if pairs * -(-vdim // 32) >= sm_count() else (16 if pairs * -(-vdim // 16) >= sm_count() else 8)
+    if ctx.max_q_len > 1:
+        vs = 32
+    else:
+        vs = 32 if pairs * -(-vdim // 32) >= sm_count() else (16 if pairs * -(-vdim // 16) >= sm_count() else 8)
     vs = min(vs, max(8, 1 << (vdim - 1).bit_length()))
     _check(lib("linear_state").lab_decay_scan(
         _ptr(out), out.stride(0), _ptr(q), _ptr(k), q.stride(0), _ptr(v), v.stride(0), _ptr(a_tok), _ptr(s_tok), ld_a,
