@@ -274,9 +274,13 @@ __global__ void __launch_bounds__(kThreads) ssm_prepare_kernel(float* __restrict
   pdl_wait();
   const int t = blockIdx.x, r = p.row_req[t], first = p.q_start[r], slot = p.state_slot[r];
   const int K = p.taps, C = p.channels;
+  // grid (rows, blocks of channels): a thread forms one channel, so that a row's loads are all in flight at
+  // once (a step of few rows is bound by their latency); the first block of a row also forms its step sizes
+  const int c = blockIdx.y * kThreads + threadIdx.x;
+  const bool heads_too = blockIdx.y == 0;
   if (slot == -1) {       // a row of padding
-    for (int c = threadIdx.x; c < C; c += kThreads) conv_out[(size_t)t * C + c] = 0.f;
-    for (int h = threadIdx.x; h < p.H; h += kThreads) dt_out[(size_t)t * p.H + h] = a_out[(size_t)t * p.H + h] = 0.f;
+    if (c < C) conv_out[(size_t)t * C + c] = 0.f;
+    for (int h = threadIdx.x; heads_too && h < p.H; h += kThreads) dt_out[(size_t)t * p.H + h] = a_out[(size_t)t * p.H + h] = 0.f;
     return;
   }
   if (slot < 0 || slot >= p.n_slots) {
@@ -284,7 +288,7 @@ __global__ void __launch_bounds__(kThreads) ssm_prepare_kernel(float* __restrict
     return;
   }
   const float* kept = p.kept + (size_t)slot * (K - 1) * C;
-  for (int c = threadIdx.x; c < C; c += kThreads) {
+  if (c < C) {
     float acc = to_f32(taps_b[c]);
     for (int jj = 0; jj < K; ++jj) {
       const int src = t - (K - 1) + jj;       // the last tap meets the row itself
@@ -294,15 +298,15 @@ __global__ void __launch_bounds__(kThreads) ssm_prepare_kernel(float* __restrict
     }
     conv_out[(size_t)t * C + c] = silu_f(acc);
   }
-  for (int h = threadIdx.x; h < p.H; h += kThreads) {
+  for (int h = threadIdx.x; heads_too && h < p.H; h += kThreads) {
     const float dt = softplus_f(p.proj[(size_t)t * p.ld + p.dt_at + h] + to_f32(dt_bias[h]));
     dt_out[(size_t)t * p.H + h] = dt;
     a_out[(size_t)t * p.H + h] = expf(-expf(to_f32(a_log[h])) * dt);
   }
 }
 
-// One block per request, after every row of the step has read the kept inputs.  A thread walks the
-// kept rows of its channel oldest first: what it overwrites it has already moved.
+// grid (requests, blocks of channels), after every row of the step has read the kept inputs.  A thread walks
+// the kept rows of its one channel oldest first: what it overwrites it has already moved.
 __global__ void __launch_bounds__(kThreads) ssm_keep_inputs_kernel(SsmParams p, int requests) {
   pdl_trigger();
   pdl_wait();
@@ -315,11 +319,12 @@ __global__ void __launch_bounds__(kThreads) ssm_keep_inputs_kernel(SsmParams p, 
   }
   const int K1 = p.taps - 1, C = p.channels;
   float* kept = p.kept + (size_t)slot * K1 * C;
-  for (int c = threadIdx.x; c < C; c += kThreads)
-    for (int i = 0; i < K1; ++i) {
-      const int s = n - K1 + i;               // the step's row that becomes kept row i
-      kept[(size_t)i * C + c] = s >= 0 ? p.proj[(size_t)(first + s) * p.ld + p.conv_at + c] : kept[(size_t)(i + n) * C + c];
-    }
+  const int c = blockIdx.y * kThreads + threadIdx.x;
+  if (c >= C) return;
+  for (int i = 0; i < K1; ++i) {
+    const int s = n - K1 + i;               // the step's row that becomes kept row i
+    kept[(size_t)i * C + c] = s >= 0 ? p.proj[(size_t)(first + s) * p.ld + p.conv_at + c] : kept[(size_t)(i + n) * C + c];
+  }
 }
 
 // ---- gate and norm of the heads' outputs ------------------------------------------------------
@@ -409,16 +414,19 @@ LAB_EXPORT int lab_ssm_prepare(float* conv_out, float* dt_out, float* a_out, con
   SsmParams p;
   p.proj = proj; p.ld = ld; p.conv_at = conv_at; p.dt_at = dt_at; p.channels = channels; p.taps = taps; p.H = H;
   p.kept = kept; p.row_req = row_req; p.q_start = q_start; p.state_slot = state_slot; p.n_slots = n_slots;
+  const int c_blocks = (channels + kThreads - 1) / kThreads;
+  if (c_blocks > 65535) return (int)cudaErrorInvalidValue;
   cudaError_t e;
   if (dtype == LAB_F32)
-    e = lab_launch(ssm_prepare_kernel<float>, dim3(tokens), dim3(kThreads), 0, stream, conv_out, dt_out, a_out,
+    e = lab_launch(ssm_prepare_kernel<float>, dim3(tokens, c_blocks), dim3(kThreads), 0, stream, conv_out, dt_out, a_out,
                    (const float*)taps_w, (const float*)taps_b, (const float*)dt_bias, (const float*)a_log, p);
   else
-    e = lab_launch(ssm_prepare_kernel<__nv_bfloat16>, dim3(tokens), dim3(kThreads), 0, stream, conv_out, dt_out, a_out,
+    e = lab_launch(ssm_prepare_kernel<__nv_bfloat16>, dim3(tokens, c_blocks), dim3(kThreads), 0, stream, conv_out, dt_out, a_out,
                    (const __nv_bfloat16*)taps_w, (const __nv_bfloat16*)taps_b, (const __nv_bfloat16*)dt_bias,
                    (const __nv_bfloat16*)a_log, p);
   if (e != cudaSuccess) return (int)e;
-  if (write && taps > 1) return (int)lab_launch(ssm_keep_inputs_kernel, dim3(requests), dim3(kThreads), 0, stream, p, requests);
+  if (write && taps > 1)
+    return (int)lab_launch(ssm_keep_inputs_kernel, dim3(requests, c_blocks), dim3(kThreads), 0, stream, p, requests);
   return 0;
 }
 
