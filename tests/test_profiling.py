@@ -55,7 +55,7 @@ def test_block_and_model_name_their_scopes(recorder):
     model.embedding, model.final_norm, model.head, model.blocks = _Stub("e"), _Stub("n"), _Stub("h"), blocks
     model.order = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2))       # layer 0 named twice
     model.range_names = [f"layer.{c.layer}" for c in model.order]
-    ctx = types.SimpleNamespace(token_ids=torch.zeros(3))
+    ctx = types.SimpleNamespace(token_ids=torch.zeros(3), row_pos=torch.arange(3))
     caches = [types.SimpleNamespace(write=True)] * 3
     out = model.forward(ctx, caches, torch.tensor([2]))
     assert out is not None
