@@ -97,3 +97,48 @@ def make_ctx(q_lens, pos0, slots, page_size=4, num_pages=64, shuffle=None, dtype
                       state_slot=t(slots), groups=[group], q_lens=list(q_lens), kv_lens=kv, state_slots=list(slots),
                       max_q_len=max(q_lens), max_kv_len=max(kv))
     return ctx, table
+
+
+def random_config(rng):
+    """A random Ritizen configuration and page size: one to five layers in any order of the three mixers, key and
+    value sizes that are multiples of 8 or only of 2 and differ from one another, any number of heads and groups,
+    chunks from one position to longer than the sequences, one to five taps, widths and feed-forwards that are
+    multiples of 8 or only of 2, layers that borrow the keys and values of an earlier attention layer."""
+    def size(lo, hi):
+        return int(rng.choice([8, 8, 16, 2])) * int(rng.integers(lo, hi))
+
+    def att():
+        G = int(rng.choice([1, 1, 2, 3]))
+        dim = min(size(1, 12), 160)
+        return attention(G * int(rng.choice([1, 2, 4, 5])), G, dim, dim if rng.random() < 0.4 else min(size(1, 12), 160),
+                         scale=float(rng.uniform(0.5, 2.0)) * dim ** -0.5)
+
+    width = size(3, 16)
+    layers, owners = [], []
+    for i in range(int(rng.integers(1, 6))):
+        ff = size(2, 20) if rng.random() < 0.7 else None
+        kind = rng.choice(["attention", "attention", "parallel", "mamba2"])
+        if kind == "attention":
+            if owners and rng.random() < 0.4:
+                src = int(rng.choice(owners))
+                m = layers[src]["mixer"]
+                layer = attention(m["heads"], m["kv_heads"], m["dim"], m["vdim"], scale=m["scale"] * 1.3, kv_from=src, ff=ff)
+            else:
+                layer = att()
+                layer["mlp"] = None if ff is None else {"kind": "dense", "ff": ff}
+                owners.append(i)
+        elif kind == "parallel":
+            heads = int(rng.choice([1, 2, 3, 6]))
+            layer = parallel(att(), int(rng.choice([1, 3, 8, 16, 33, 64, 500])), heads, min(size(1, 10), 96), size(1, 8),
+                             [float(d) for d in rng.uniform(0.3, 1.0, size=heads)],
+                             scales=(float(rng.uniform(0.2, 1.5)), float(rng.uniform(0.2, 1.5))), ff=ff)
+        else:
+            groups = int(rng.choice([1, 1, 2, 3]))
+            heads, vdim, parts = groups * int(rng.choice([1, 2, 4])), size(1, 8), int(rng.choice([1, 1, 2]))
+            if (heads * vdim) % parts:
+                parts = 1
+            layer = mamba2(heads, vdim, min(size(1, 12), 128), groups, int(rng.integers(1, 6)), parts, ff=ff)
+        layers.append(layer)
+    cfg = config(layers, vocab=int(rng.integers(30, 400)), width=width, max_positions=int(rng.choice([160, 260])),
+                 eps=float(rng.choice([1e-6, 1e-5])))
+    return cfg, int(rng.choice([16, 16, 4, 8, 32, 64]))

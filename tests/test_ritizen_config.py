@@ -108,3 +108,14 @@ def test_plain_mechanisms_have_the_properties_the_design_names():
     ids = [int(t) for t in rng.integers(0, raw["vocab"], size=30)]
     full = pr.forward(raw, w, ids)
     assert np.abs(pr.forward(raw, w, ids[:17]) - full[:17]).max() < 1e-9
+
+
+def test_bench_configurations_are_valid():
+    import bench
+    for shape in sorted(bench.RITIZEN_SHAPES):
+        raw = bench.ritizen_config(shape, 4)
+        arch, cfg = _cfg(raw)
+        assert [layer["type"] for layer in raw["layers"]] == ["attention", "attention", "mamba2", "parallel"]
+        assert cfg.width == bench.SHAPES[shape]["hidden_size"] and raw["layers"][1]["mixer"]["kv_from"] == 0
+        from llm_inference_lab_b200.models.builder import expected_tensors
+        assert len(expected_tensors(arch.blueprint(cfg))) > 40

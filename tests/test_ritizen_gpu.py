@@ -8,7 +8,8 @@ import pytest
 import plain_ritizen as pr
 from helpers import (error_stats, make_model_folder, run_trace_inprocess, run_trace_program, tokens_needed,
                      trace_mixed, trace_portions, trace_tail_decode, trace_whole)
-from ritizen_helpers import (SMALL, SPREAD, attention, config, make_ctx, mamba2, parallel, plain_logits, sequences)
+from ritizen_helpers import (SMALL, SPREAD, attention, config, make_ctx, mamba2, parallel, plain_logits,
+                             random_config, sequences)
 
 pytestmark = pytest.mark.gpu
 
@@ -466,6 +467,31 @@ def test_long_portions_and_long_decoding(tmp_path):
                          ("mixed", trace_mixed(seqs, np.random.default_rng(2), max_live=3, max_portion=140))):
         eng = _engine(folder, "bfloat16", opt, steps)
         _check(run_trace_inprocess(eng, steps), want, "bfloat16", label)
+
+
+@pytest.mark.parametrize("trial", range(int(os.environ.get("LAB_RANDOM_RITIZEN", "6"))))
+def test_random_configurations_and_traces(tmp_path, trial):
+    """Random configurations (layer orders, sizes that are no multiples of 8 or 16, key sizes that differ from
+    value sizes, chunks of 1 to 500 positions, 1 to 5 taps, borrowed keys and values, page sizes 4 to 64) under
+    mixed batches with pages and slots used again, in both storage types.  `LAB_RANDOM_RITIZEN=N` runs N."""
+    rng = np.random.default_rng(1000 + trial)
+    cfg, page = random_config(rng)
+    seqs = sequences(rng, cfg["vocab"], [int(n) for n in rng.integers(1, 150, size=6)])
+    steps = trace_mixed(seqs, np.random.default_rng(trial), max_live=4, max_portion=int(rng.choice([9, 40, 140])))
+    want = None
+    for dtype in ("float32", "bfloat16"):
+        folder = make_model_folder(str(tmp_path / dtype), cfg, trial, dtype, std=0.08, scales=SPREAD)
+        if want is None or dtype == "bfloat16":
+            want = plain_logits(folder, seqs)
+        eng = _engine(folder, dtype, dict(page_size=page), steps)
+        got = run_trace_inprocess(eng, steps)
+        worst, rms, where = error_stats(got, want)
+        if dtype == "float32":
+            assert worst < F32_MAX, (trial, cfg, worst, where)
+        else:
+            depth = len(cfg["layers"])
+            assert rms < BF16_RMS * (1 + 0.25 * max(0, depth - 3)), (trial, cfg, worst, rms, where)
+        assert eng.cache.live_requests == 0
 
 
 def test_cuts_agree_in_32_bit(tmp_path):
