@@ -383,6 +383,35 @@ def test_decay_linear_attention_part_against_plain(heads, dim, vdim):
         at += n
 
 
+def test_side_by_side_takes_any_mixers():
+    """Mixers that cannot share products (here another design's recurrent mixer beside the linear attention) run
+    one after the other and are summed with their constants; each keeps its own part of the cache."""
+    torch = _torch()
+    from llm_inference_lab_b200.parts import CacheView, PartSpec
+    rng = np.random.default_rng(2)
+    lin = PartSpec("decay_linear_attention", {"hidden": 40, "heads": 2, "dim": 16, "vdim": 8, "decay": (0.9, 0.6),
+                                              "eps": 1e-5}, prefix="a.")
+    other = PartSpec("general_delta", {"hidden": 40, "heads": 2, "dim": 16, "eps": 1e-5, "decay_rate": 0.6,
+                                       "decay_rank": 8}, prefix="b.")
+    both = PartSpec("side_by_side", {"hidden": 40, "parts": ((lin, 0.5), (other, 2.0))}, prefix="")
+    mixer, _ = _mixer(both, 0.2, torch.float32, 6)
+    assert not mixer.shared and mixer.decode_graph_safe
+
+    def views():
+        return [CacheView(None, state=torch.zeros((1, 2, 16, 8), device="cuda:0")),
+                CacheView(None, state=torch.zeros((1, 2, 16, 16), device="cuda:0"))]
+
+    h = _t(rng.standard_normal((12, 40)))
+    ctx, _ = make_ctx([12], [0], [0])
+    apart = views()
+    a, b = (m.forward(h, ctx, v) for (m, _), v in zip(mixer.mixers, apart))
+    want = 0.5 * (_np(a).sum(0) if a.dim() == 3 else _np(a)) + 2.0 * (_np(b).sum(0) if b.dim() == 3 else _np(b))
+    together = CacheView(None, parts=views())
+    got = mixer.forward(h, ctx, together)
+    assert got.dim() == 2 and np.abs(_np(got) - want).max() < 1e-5
+    assert all(torch.equal(x.state, y.state) for x, y in zip(apart, together.parts))
+
+
 # ---------------------------------------------------------------------------------------------
 # whole models under every cut
 # ---------------------------------------------------------------------------------------------
