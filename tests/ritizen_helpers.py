@@ -48,8 +48,8 @@ SMALL_C = config([mamba2(1, 20, 16, 1, 1, 1, ff=30), attention(1, 1, 48, 48), at
                   parallel(attention(1, 1, 16, 16), 32, 1, 8, 8, (0.8,), ff=44)],
                  vocab=67, width=50, max_positions=160, eps=3e-6)
 # D: heads of 64 and 128 entries (the sizes the tcgen05 attention is built for) with long portions
-SMALL_D = config([attention(4, 2, 64, 64, ff=64), parallel(attention(2, 1, 128, 128), 96, 2, 32, 32, (0.9, 0.999))],
-                 vocab=113, width=64, max_positions=448)
+SMALL_D = config([attention(6, 3, 64, 64, ff=64), parallel(attention(2, 1, 128, 128), 96, 2, 32, 32, (0.9, 0.999))],
+                 vocab=113, width=64, max_positions=464)
 SMALL = {"A": (SMALL_A, dict(seed=11, page_size=16)), "B": (SMALL_B, dict(seed=12, page_size=4)),
          "C": (SMALL_C, dict(seed=13, page_size=32)), "D": (SMALL_D, dict(seed=14, page_size=16))}
 

@@ -69,7 +69,7 @@ def test_stream_operators_against_numpy():
         assert np.abs(_np(ops.gelu_tanh_(z.clone())) - ref).max() < (1e-6 if dtype == torch.float32 else 2e-2)
 
 
-@pytest.mark.parametrize("tokens,n_out,k", [(3, 200, 64), (70, 96, 320), (300, 520, 128), (4100, 512, 2048),
+@pytest.mark.parametrize("tokens,n_out,k", [(3, 200, 64), (70, 96, 328), (300, 520, 128), (4100, 512, 2112),
                                             (9, 50, 36), (200, 30, 100)])
 def test_gelu_in_the_products_epilogue(tokens, n_out, k):
     """The activation as the epilogue of the up product (both orientations of the tensor-core kernel, the
@@ -83,14 +83,14 @@ def test_gelu_in_the_products_epilogue(tokens, n_out, k):
             _t(rng.standard_normal(n_out), dtype)
         fused = ops.linear(x, w, b, act="gelu_tanh")
         ref = pr.gelu_tanh(_np(x) @ _np(w).T + _np(b))
-        assert fused.dtype == dtype and np.abs(_np(fused) - ref).max() < (2e-2 if dtype == torch.bfloat16 else 1e-5)
+        assert fused.dtype == dtype and np.abs(_np(fused) - ref).max() < (2e-2 if dtype == torch.bfloat16 else 3e-5)
         two = ops.gelu_tanh_(ops.linear(x, w, b, out_f32=True)).to(dtype)     # one rounding, as in the epilogue
         assert torch.equal(fused, two)
     with pytest.raises(ops.KernelError):
         ops.linear(x, w, b, act="relu")
 
 
-@pytest.mark.parametrize("dims", [(3, 1, 16, 24), (2, 2, 40, 8), (4, 2, 64, 64)])
+@pytest.mark.parametrize("dims", [(3, 1, 16, 24), (2, 2, 40, 8), (6, 3, 64, 64)])
 def test_whole_projection_norms_cache_store_and_gates(dims):
     """q and k normed over all heads at once (not head by head), heads stored with zero padding, k and v in the
     rows' page slots only, rows of padding skipped; both kinds of gate; partial products and a bias."""
@@ -253,7 +253,7 @@ def _plain_recurrence(q, k, v, a, s, S0):
     return out, S
 
 
-@pytest.mark.parametrize("H,G,N,V", [(3, 3, 20, 12), (4, 2, 48, 48), (1, 1, 5, 33), (2, 1, 130, 7)])
+@pytest.mark.parametrize("H,G,N,V", [(3, 3, 20, 12), (4, 2, 40, 56), (1, 1, 5, 33), (2, 1, 130, 7)])
 def test_decay_scan_against_plain(H, G, N, V):
     """The recurrence alone: requests of unequal lengths side by side in portions of changing size down to
     single tokens, state slots that hold stale numbers of other requests, a fixed decay per head (with the
@@ -361,7 +361,7 @@ def test_state_space_part_against_plain(taps, groups, parts):
         assert all(torch.all(part.state[1] == 9.0) for part in view.parts)
 
 
-@pytest.mark.parametrize("heads,dim,vdim", [(3, 20, 12), (1, 64, 32), (2, 8, 40)])
+@pytest.mark.parametrize("heads,dim,vdim", [(3, 20, 12), (1, 64, 24), (2, 8, 40)])
 def test_decay_linear_attention_part_against_plain(heads, dim, vdim):
     torch = _torch()
     from llm_inference_lab_b200.parts import CacheView, PartSpec
@@ -441,7 +441,7 @@ ONE_LAYER = {
     "attention": config([attention(4, 2, 16, 16, ff=None)], vocab=53, width=32),
     "attention+ff": config([attention(3, 1, 24, 8, ff=48)], vocab=53, width=40),
     "borrowed": config([attention(2, 2, 32, 16), attention(2, 2, 32, 16, kv_from=0)], vocab=53, width=32),
-    "mamba2": config([mamba2(2, 16, 8, 2, 3, 2)], vocab=53, width=32),
+    "mamba2": config([mamba2(2, 16, 8, 2, 5, 1)], vocab=53, width=32),
     "mamba2+ff": config([mamba2(3, 8, 24, 1, 4, 3, ff=40)], vocab=53, width=24),
     "parallel": config([parallel(attention(2, 1, 16, 16), 12, 2, 24, 8, (0.7, 0.97))], vocab=53, width=32),
     "parallel+ff": config([parallel(attention(4, 4, 8, 24), 5, 1, 16, 16, (0.9,), scales=(0.2, 2.0), ff=56)],
